@@ -103,6 +103,8 @@ class CacheManager:
         self.groups: List[Group] = []
         self.entries: List[EntryCache] = []
         self.live: Dict[int, RequestCache] = {}
+        # requirements behind the schedule's (the model's own parts with state) own their caches
+        cache_from = list(cache_from) + [None] * (len(requirements) - len(cache_from))
         by_key: Dict[PagedKV, int] = {}
         for i, req in enumerate(requirements):
             if cache_from[i] is not None:

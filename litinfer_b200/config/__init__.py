@@ -1,3 +1,4 @@
+from .demavik import DemavikConfig
 from .filasun import FilasunConfig
 from .gorulorn import GorulornConfig
 from .qwen2 import ConfigError, Qwen2Config
@@ -14,6 +15,7 @@ from .spec import BlockSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedul
 __all__ = [
     "BlockSpec",
     "ConfigError",
+    "DemavikConfig",
     "FilasunConfig",
     "GorulornConfig",
     "ModelSpec",

@@ -13,6 +13,7 @@ import json
 from pathlib import Path
 from typing import Any, Dict, Mapping, Type
 
+from .demavik import DemavikConfig
 from .filasun import FilasunConfig
 from .gorulorn import GorulornConfig
 from .qwen2 import ConfigError, Qwen2Config
@@ -55,7 +56,25 @@ def load_config(model_dir):
         path = path / "config.json"
     if not path.is_file():
         raise FileNotFoundError(f"config.json not found: {path}")
-    return config_from_dict(json.loads(path.read_text()))
+    d = json.loads(path.read_text())
+    archs = d.get("architectures") or d.get("architecture")
+    cls = _ARCHITECTURES.get(archs if isinstance(archs, str) else (archs[0] if archs else None))
+    if cls is not None and hasattr(cls, "sizes_from_tensors"):
+        # a design may leave a size to the shape of a tensor: the configuration class is shown the stored shapes
+        d = cls.sizes_from_tensors(d, _stored_shapes(path.parent))
+    return config_from_dict(d)
+
+
+def _stored_shapes(model_dir: Path) -> Dict[str, tuple]:
+    """name -> shape of every tensor in the folder's safetensors files (headers only); empty if there are none."""
+    from ..weights.safetensors_io import read_header
+
+    out: Dict[str, tuple] = {}
+    for f in sorted(model_dir.glob("*.safetensors")):
+        header, _ = read_header(f)
+        for n, info in header.items():
+            out[n] = tuple(info["shape"])
+    return out
 
 
 def model_spec_from_dir(model_dir) -> ModelSpec:
@@ -65,3 +84,4 @@ def model_spec_from_dir(model_dir) -> ModelSpec:
 register_architecture(Qwen2Config.ARCHITECTURE, Qwen2Config)
 register_architecture(FilasunConfig.ARCHITECTURE, FilasunConfig)
 register_architecture(GorulornConfig.ARCHITECTURE, GorulornConfig)
+register_architecture(DemavikConfig.ARCHITECTURE, DemavikConfig)

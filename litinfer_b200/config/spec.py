@@ -133,6 +133,9 @@ class ModelSpec:
     streams: Optional[int] = None
     # tables of vectors that schedule entries add to the residual stream (``ScheduleEntry.add``): tensor name -> rows
     stream_tables: Mapping[str, int] = field(default_factory=dict)
+    # parts that add something to the residual stream right after the embedding and may keep a state per request for it
+    # (an embedding of token pairs): (spec, tensor-name prefix) each, kinds of the registry of stream inputs
+    stream_inputs: Tuple[Tuple[PartSpec, str], ...] = ()
     # other names under which a declared tensor may be stored: declared name -> names tried after it
     aliases: Mapping[str, Tuple[str, ...]] = field(default_factory=dict)
 

@@ -24,6 +24,36 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
     for (int j = threadIdx.x; j < H; j += blockDim.x) dst[j] = to_float(row[j]);
 }
 
+// x[t] += pairs[row of (previous token, token)]; the previous token of a portion's first token is the sequence's state.
+template <typename T>
+__global__ void add_pair_rows_kernel(float* __restrict__ x, const T* __restrict__ pairs, const int* __restrict__ ids,
+                                     const int* __restrict__ positions, const int* __restrict__ q_start, const int* __restrict__ seq_of_token,
+                                     const int* __restrict__ slots, int* __restrict__ state, long long state_stride, int buckets,
+                                     long long mul_prev, long long mul_cur, int H) {
+    __shared__ int row_s;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const int s = seq_of_token[t];
+        const int first = q_start[s], end = q_start[s + 1];
+        int* st = state + (size_t)slots[s] * state_stride;
+        int row = buckets;                                      // a sequence's first token
+        if (positions[t] > 0) {
+            const long long prev = t > first ? ids[t - 1] : *st;
+            long long r = (prev * mul_prev + (long long)ids[t] * mul_cur) % buckets;
+            row = (int)(r < 0 ? r + buckets : r);
+        }
+        // the portion's first token is the only reader of the state, so it also moves it on: to the portion's last token
+        if (t == first) *st = ids[end - 1];
+        row_s = row;
+    }
+    __syncthreads();
+    const T* src = pairs + (size_t)row_s * H;
+    float* dst = x + (size_t)t * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) dst[j] += to_float(src[j]);
+}
+
 // mode 0: y = norm(x[row]); mode 1: x[row] += delta[row] first (stored back).
 template <typename T, bool kAdd>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
@@ -142,6 +172,22 @@ int grid_for(long long n, int threads) {
 }
 
 }  // namespace
+
+LI_EXPORT int li_add_pair_rows(float* x, const void* pairs, int dtype, const int* ids, const int* positions, const int* q_start,
+                               const int* seq_of_token, const int* slots, int* state, long long state_stride, int buckets, long long mul_prev,
+                               long long mul_cur, int T, int H, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && H > 0 && buckets > 0 && state_stride > 0, "add_pair_rows: bad sizes T=%d H=%d buckets=%d", T, H, buckets);
+    if (T == 0) return 0;
+    if (dtype == LI_F32)
+        li_launch_pdl(add_pair_rows_kernel<float>, dim3(T), dim3(kRowThreads), 0, stream, x, (const float*)pairs, ids, positions, q_start, seq_of_token,
+                      slots, state, state_stride, buckets, mul_prev, mul_cur, H);
+    else if (dtype == LI_BF16)
+        li_launch_pdl(add_pair_rows_kernel<bf16>, dim3(T), dim3(kRowThreads), 0, stream, x, (const bf16*)pairs, ids, positions, q_start, seq_of_token,
+                      slots, state, state_stride, buckets, mul_prev, mul_cur, H);
+    else
+        return li_fail("add_pair_rows: unknown dtype %d", dtype);
+    return li_check_launch("add_pair_rows");
+}
 
 LI_EXPORT int li_embedding(const void* table, int dtype, const int* ids, float* out, int T, int H, int V, cudaStream_t stream) {
     LI_REQUIRE(T >= 0 && H > 0 && V > 0, "embedding: bad sizes T=%d H=%d V=%d", T, H, V);

@@ -11,7 +11,8 @@
 //     128 rows and number 256 or more go to tcgen05 tiles (gemm_tcgen05.cu).  Either way float accumulation, each output summed over k in ascending
 //     order by one thread: a row's result does not depend on which rows stand beside it.
 //   li_moe_route:   scores = sigmoid(logits), the `top` largest per token (the lower index wins a tie); the scores of the
-//     chosen are the weights as they are, not renormalised.
+//     chosen are the weights as they are, not renormalised.  Or the largest logits choose, and the weights are the softmax
+//     over the chosen logits alone.
 //   li_moe_sort:    a stable counting sort of the (token, choice) pairs by expert: offsets per expert, the pair at each
 //     sorted place, and each pair's place.  One block per expert walks the pairs in order, so the result is the same
 //     whatever runs beside it.
@@ -238,7 +239,8 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, int a_gcol, const bf16* 
 
 constexpr int kMaxExpertsPerLane = 8;       // experts <= 256
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int* __restrict__ ids, float* __restrict__ weights) {
+__global__ void moe_route_kernel(const float* __restrict__ logits, int scoring, int T, int E, int top, int* __restrict__ ids,
+                                 float* __restrict__ weights) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -248,10 +250,14 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
 #pragma unroll
     for (int i = 0; i < kMaxExpertsPerLane; ++i) {
         const int e = lane + 32 * i;
-        s[i] = e < E ? 1.0f / (1.0f + expf(-logits[(size_t)t * E + e])) : -1.0f;      // scores lie in (0, 1): -1 never wins
+        const float z = e < E ? logits[(size_t)t * E + e] : 0.0f;
+        // sigmoid scores lie in (0, 1): -1 never wins; logits taken as they are: the lowest float never wins
+        if (scoring == 0) s[i] = e < E ? 1.0f / (1.0f + expf(-z)) : -1.0f;
+        else s[i] = e < E ? fmaxf(z, -3.0e38f) : -3.4e38f;
     }
+    const float gone = scoring == 0 ? -1.0f : -3.4e38f;
     for (int k = 0; k < top; ++k) {
-        float best = -2.0f;
+        float best = scoring == 0 ? -2.0f : -INFINITY;
         int arg = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < kMaxExpertsPerLane; ++i) {
@@ -270,7 +276,15 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
         }
 #pragma unroll
         for (int i = 0; i < kMaxExpertsPerLane; ++i)
-            if (lane + 32 * i == arg) s[i] = -1.0f;
+            if (lane + 32 * i == arg) s[i] = gone;
+    }
+    if (scoring == 1 && lane == 0) {
+        // the weights are the softmax over the chosen logits alone (the first chosen is the largest)
+        float* wt = weights + (size_t)t * top;
+        const float m = wt[0];
+        float sum = 0.0f;
+        for (int k = 0; k < top; ++k) sum += expf(wt[k] - m);
+        for (int k = 0; k < top; ++k) wt[k] = expf(wt[k] - m) / sum;
     }
 }
 
@@ -427,11 +441,14 @@ LI_EXPORT int li_grouped_linear(const void* a, int lda, int a_gcol, const void* 
     return li_check_launch("grouped_linear");
 }
 
-LI_EXPORT int li_moe_route(const float* logits, int T, int E, int top, int* ids, float* weights, cudaStream_t stream) {
+// scoring 0: the scores are sigmoid(logits) and the chosen experts' scores are their weights; 1: the largest logits choose and
+// the weights are the softmax over the chosen logits alone.
+LI_EXPORT int li_moe_route(const float* logits, int scoring, int T, int E, int top, int* ids, float* weights, cudaStream_t stream) {
     LI_REQUIRE(T >= 0 && E > 0 && top > 0 && top <= E, "moe_route: %d of %d experts", top, E);
+    LI_REQUIRE(scoring == 0 || scoring == 1, "moe_route: unknown scoring %d", scoring);
     LI_REQUIRE(E <= 32 * kMaxExpertsPerLane, "moe_route: %d experts are more than %d", E, 32 * kMaxExpertsPerLane);
     if (T == 0) return 0;
-    const cudaError_t e = li_launch_pdl(moe_route_kernel, dim3(ceil_div(T, 4)), dim3(128), 0, stream, logits, T, E, top, ids, weights);
+    const cudaError_t e = li_launch_pdl(moe_route_kernel, dim3(ceil_div(T, 4)), dim3(128), 0, stream, logits, scoring, T, E, top, ids, weights);
     if (e != cudaSuccess) return li_fail("moe_route: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("moe_route");
 }

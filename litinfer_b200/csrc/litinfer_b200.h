@@ -66,6 +66,14 @@ int li_decode_step(const LiDecodeStep* step, cudaStream_t stream);
 /* out[t] = table[ids[t]] as float. */
 int li_embedding(const void* table, int dtype, const int* ids, float* out, int T, int H, int V, cudaStream_t stream);
 
+/* x[t] += pairs[row] with row = (prev * mul_prev + ids[t] * mul_cur) mod buckets, prev the token before t in its sequence:
+ * ids[t - 1] inside a portion, for a portion's first token the sequence's last token of the step before (state [slots,
+ * state_stride] int32, element 0), and row `buckets` for a sequence's first token (position 0).  The state moves on to the
+ * portion's last token in the same launch.  pairs [buckets + 1, H] in the run dtype. */
+int li_add_pair_rows(float* x, const void* pairs, int dtype, const int* ids, const int* positions, const int* q_start,
+    const int* seq_of_token, const int* slots, int* state, long long state_stride, int buckets, long long mul_prev, long long mul_cur,
+    int T, int H, cudaStream_t stream);
+
 /* out = x / sqrt(mean(x^2) + eps) * w, rows of H; out in the run dtype. */
 int li_rmsnorm(const float* x, const float* w, float eps, void* out, int dtype, int T, int H, cudaStream_t stream);
 
@@ -149,10 +157,27 @@ int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, 
  * triples of first chunk, chunks, slot; a chunk's decay given, or token_decay[head] ^ length) turns chunk_state into the states the chunks start from and moves the slots on,
  * then the scans with mode 2 (outputs).  Mode 0 without seg: every sequence in one piece. */
 int li_scan_carry(float* state, long long state_stride, float* chunk_state, const float* chunk_decay, const float* token_decay,
-    const int* seg, const int* runs, int nruns, int heads, int per_head, cudaStream_t stream);
+    const int* seg, const int* runs, int nruns, int heads, int per_head, int period, cudaStream_t stream);
+
+/* Per head S [d, dv] with a decay per token and key channel: S = diag(a) S + k v^T, out = S^T (q q_scale), with
+ * a = sigmoid(z)^inv_tau from the float logits za [T, za_stride] at column za_off (heads x d); q, k, v are the columns at
+ * q_off, k_off, v_off of qkv [T, stride] as they are; the state is kept as [heads][dv][d]; chunk_decay [chunks, heads, d]
+ * (li_scan_carry with period d). */
+int li_gla_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const float* za, int za_stride, int za_off,
+    float inv_tau, float q_scale, float* state, long long state_stride, const int* q_start, const int* slots, float* out,
+    int S, int heads, int d, int dv, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream);
+
+/* Per channel c a state S [N]: S = exp(dt_c A[c, :]) S + dt_c x_c B, y_c = (S . C + D[c] x_c) silu(z_c), with
+ * dt = softplus(dt_raw) (float, [T, dt_stride]), A = -exp(A_log) [inner, N]; x at column x_off of [T, x_stride], B and C
+ * (N each) at b_off and c_off of bc [T, bc_stride], the gate z at z_off of [T, z_stride]; y [T, inner] in the run dtype; the
+ * state is kept as [inner][N]; chunk_decay [chunks, inner, N] (li_scan_carry with one head and period inner N). */
+int li_channel_scan(const void* x, int dtype, int x_stride, int x_off, const void* bc, int bc_stride, int b_off, int c_off,
+    const float* dt_raw, int dt_stride, const void* z, int z_stride, int z_off, const float* A_log, const float* D,
+    float* state, long long state_stride, const int* q_start, const int* slots, void* y, int S, int inner, int N,
+    const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream);
 
 /* RMSNorm of y [T, n] (float) in `groups` equal parts, times w; mode 0: y is first multiplied by silu(gate), mode 1:
- * the result is multiplied by sigmoid(gate); gate [T, gate_stride] at column gate_off, in the run dtype like out. */
+ * the result is multiplied by sigmoid(gate), mode 2: by silu(gate); gate [T, gate_stride] at column gate_off, in the run dtype like out. */
 int li_gated_rmsnorm(const float* y, const void* gate, int dtype, int gate_stride, int gate_off, const float* w, float eps, int mode,
     void* out, int T, int n, int groups, cudaStream_t stream);
 
@@ -218,7 +243,7 @@ int li_linear_rope_kv(const void* a, const void* w, const float* bias, void* qkv
 
 /* ---- norm_pair.cu: norms before and after a sublayer in one pass over the residual stream ---- */
 /* Per row: x += post(y) (post: a norm of y [R, H] with the weight w_post; NULL: x += y; y NULL: nothing is added), then
- * out = next(x) if w_next is given.  A norm is centered (mean taken off, variance as the mean of squared deviations:
+ * out = next(x) if w_next is given (without it, out, if given, takes x as it is in the run dtype).  A norm is centered (mean taken off, variance as the mean of squared deviations:
  * layer norm without bias) or not (RMS norm).  rows (may be NULL; only without y): out[r] = next(x[rows[r]]).
  * y_places (may be NULL): token r's y is the sum over j < y_top of y[y_places[r y_top + j]] (times y_weights[...] if given). */
 int li_norm_add_norm(float* x, const void* y, int dtype, const float* w_post, int post_centered, float eps_post, const float* w_next,
@@ -237,13 +262,21 @@ int li_rmsnorm_cols(const void* in, int dtype, int ld_in, int col, int n, int wi
 /* A short causal convolution per channel (conv_w [(nh + 2 nkv) dh, taps]; inputs before a portion from state [slots,
  * state_stride] at state_off), an RMS norm per query and key head (q_norm, k_norm [dh], mean over norm_width elements),
  * the rotation of the first rotary_dim elements, q to out, k and v into the paged cache.  Every step is optional.
+ * row_rinv (may be NULL) [T, 2]: the norm is over the whole projection of q (column 0) and of k (column 1) instead: the
+ * factor is given, and q_norm [nh dh], k_norm [nkv dh] hold a weight per channel.  nkv 0 (with write 0): proj and out hold
+ * queries only.  out_ld: elements of a row of out (0: as many as a row of proj).
  * shift: every sequence of the step has one token, and the state moves on in the same launch.  to_cache 0: keys and values
  * go to their columns of out, not into the cache. */
 int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* conv_w, int taps, float* state,
     long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
-    const float* q_norm, const float* k_norm, float eps, int norm_width, const int* positions, const float* denom,
-    int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh,
-    int page_size, int num_pages, int write, int shift, int to_cache, cudaStream_t stream);
+    const float* q_norm, const float* k_norm, float eps, int norm_width, const float* row_rinv, const int* positions,
+    const float* denom, int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh,
+    int page_size, int num_pages, int write, int shift, int to_cache, int out_ld, cudaStream_t stream);
+
+/* out[t, j] = 1 / sqrt(sum of squares of the columns col_j .. col_j + n_j - 1 of x [T, ld] / width_j + eps), j = 0, 1 (n_1
+ * 0: one range): the factor of an RMS norm over a whole projection, for li_conv_norm_rope_kv's row_rinv. */
+int li_row_rinv(const void* x, int dtype, int ld, int col0, int n0, int width0, int col1, int n1, int width1, float eps, float* out,
+    int T, cudaStream_t stream);
 
 /* ---- grouped.cu: products in groups, routing of a mixture of experts ---- */
 /* out_g = a_g w_g^T, w [G, N, K].  row_offsets [G + 1] (device): group g owns those rows of a [M, lda] and out [M, ldc].
@@ -254,8 +287,9 @@ int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* co
 int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets,
     const int* tile_group, int dtype, int M, int N, int K, int G, int epilogue, cudaStream_t stream);
 
-/* ids, weights [T, top]: the experts with the largest sigmoid(logits [T, E]) and those scores. */
-int li_moe_route(const float* logits, int T, int E, int top, int* ids, float* weights, cudaStream_t stream);
+/* ids, weights [T, top]: the experts with the largest sigmoid(logits [T, E]) and those scores (scoring 0), or the experts
+ * with the largest logits and the softmax over the chosen logits alone (scoring 1). */
+int li_moe_route(const float* logits, int scoring, int T, int E, int top, int* ids, float* weights, cudaStream_t stream);
 
 /* Stable sort of n (token, choice) pairs by expert: offsets [E + 1], pair_at (pair at a sorted place, -1: none), place_of [n].
  * Every expert's run starts at a multiple of pad; pair_at has `places` entries; tile_group (may be NULL) [n_tiles]: the expert of every tile of pad rows. */

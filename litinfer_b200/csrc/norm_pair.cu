@@ -3,7 +3,8 @@
 //
 //   li_norm_add_norm: per token row
 //       x += post(y)          post: a norm of the sublayer's output y with its own weight (or none: x += y; or no y at all)
-//       out = next(x)         next: the norm that feeds the following sublayer (optional)
+//       out = next(x)         next: the norm that feeds the following sublayer (optional; without one, out may still be
+//                             asked for and is x in the run dtype: a sublayer that reads the stream itself)
 //     where a norm is  (v - mean) / sqrt(var + eps) * w  (centered: layer norm without bias, var the mean of the squared
 //     deviations) or  v / sqrt(mean(v^2) + eps) * w  (not centered: RMS norm).  Rows may be gathered (rows[r]) when
 //     there is no y: the model's last norm on the wanted rows only.
@@ -65,6 +66,10 @@ __global__ void norm_add_norm_kernel(float* __restrict__ x, const T* __restrict_
         const float rinv = row_stat_norm(xr, H, next_centered, eps_next, scratch, &mean);
         T* o = out + (size_t)r * H;
         for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<T>((xr[i] - mean) * rinv * w_next[i]);
+    } else if (out) {
+        // no following norm but an output: the row as it is, in the run dtype (a sublayer that reads the stream itself)
+        T* o = out + (size_t)r * H;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<T>(xr[i]);
     }
 }
 
@@ -233,6 +238,8 @@ __global__ void norm_add_norm_regs_kernel(float* __restrict__ x, const T* __rest
         float nv[kRegs];
         row_norm<kVec>(nv, xv, w_next, next_centered, eps_next, H, scratch);
         store_row<kVec>(out + (size_t)r * H, nv, H);
+    } else if (out) {
+        store_row<kVec>(out + (size_t)r * H, xv, H);        // the row as it is, in the run dtype
     }
 }
 
@@ -267,7 +274,8 @@ __global__ void rmsnorm_cols_kernel(const T* __restrict__ in, int ld_in, int col
 
 }  // namespace
 
-// y (may be NULL): [R, H] in the run dtype; w_post (may be NULL: x += y); w_next (may be NULL: no output); rows (may
+// y (may be NULL): [R, H] in the run dtype; w_post (may be NULL: x += y); w_next (may be NULL: no norm; out then takes the
+// row as it is, if out is given); rows (may
 // be NULL; only without y): out[r] = next(x[rows[r]]).  x is [n_src, H] float and is changed in place when y is given.
 // y_places (may be NULL; H up to 8,192): token r's y is the sum over j < y_top of y[y_places[r y_top + j]] (times
 // y_weights[r y_top + j] if given), summed in float in that order: the combine of a mixture of experts, not written out.

@@ -27,9 +27,11 @@ __global__ void __launch_bounds__(kWarps * 32)
 conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const float* __restrict__ conv_w, int taps_rt,
                          float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
                          const int* __restrict__ seq_of_token, const int* __restrict__ slots, const float* __restrict__ q_norm,
-                         const float* __restrict__ k_norm, float eps, int norm_width, const int* __restrict__ positions,
+                         const float* __restrict__ k_norm, float eps, int norm_width, const float* __restrict__ row_rinv,
+                         const int* __restrict__ positions,
                          const float* __restrict__ denom, int rotary_dim, const int* __restrict__ slot_mapping, T* __restrict__ kcache,
-                         T* __restrict__ vcache, int total, int nh, int nkv, int dh, int page_size, int num_pages, int write, int shift, int to_cache) {
+                         T* __restrict__ vcache, int total, int nh, int nkv, int dh, int page_size, int num_pages, int write, int shift, int to_cache,
+                         int out_ld) {
     extern __shared__ float smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -81,7 +83,16 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
     }
     // 2. the norm of a query or key head
     const float* nw = is_q ? q_norm : (is_k ? k_norm : nullptr);
-    if (nw) {
+    if (nw && row_rinv) {
+        // a norm over the whole projection: the factor was taken over all heads, the weight is per channel
+        const float rinv = row_rinv[2 * (size_t)t + (is_q ? 0 : 1)];
+        const float* wc = nw + (is_q ? c0 : c0 - nh * dh);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = lane + 32 * i;
+            if (i < per && d < dh) v[i] = v[i] * rinv * wc[d];
+        }
+    } else if (nw) {
         float q = 0.0f;
 #pragma unroll
         for (int i = 0; i < PER; ++i) q = fmaf(v[i], v[i], q);
@@ -118,7 +129,7 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
     }
     // 4. where it goes (keys and values of a long step stay in the row: a kernel that writes whole pieces of pages takes them from there)
     if (is_q || !to_cache) {
-        T* o = out + (size_t)t * N + c0;
+        T* o = out + (size_t)t * out_ld + c0;
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int d = lane + 32 * i;
@@ -146,28 +157,77 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
     }
 }
 
+// One block per token: the reciprocal root of the mean of squares over up to two ranges of columns.
+template <typename T>
+__global__ void row_rinv_kernel(const T* __restrict__ x, int ld, int col0, int n0, int width0, int col1, int n1, int width1, float eps,
+                                float* __restrict__ out) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* row = x + (size_t)blockIdx.x * ld;
+    float a = 0.0f, b = 0.0f;
+    for (int i = threadIdx.x; i < n0; i += blockDim.x) {
+        const float v = to_float(row[col0 + i]);
+        a = fmaf(v, v, a);
+    }
+    for (int i = threadIdx.x; i < n1; i += blockDim.x) {
+        const float v = to_float(row[col1 + i]);
+        b = fmaf(v, v, b);
+    }
+    a = block_sum(a, scratch);
+    __syncthreads();
+    b = block_sum(b, scratch);
+    if (threadIdx.x == 0) {
+        out[2 * (size_t)blockIdx.x] = 1.0f / sqrtf(a / (float)width0 + eps);
+        out[2 * (size_t)blockIdx.x + 1] = n1 > 0 ? 1.0f / sqrtf(b / (float)width1 + eps) : 0.0f;
+    }
+}
+
 }  // namespace
+
+LI_EXPORT int li_row_rinv(const void* x, int dtype, int ld, int col0, int n0, int width0, int col1, int n1, int width1, float eps, float* out,
+                          int T, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && n0 > 0 && width0 > 0 && col0 >= 0 && col0 + n0 <= ld, "row_rinv: bad first range");
+    LI_REQUIRE(n1 >= 0 && (n1 == 0 || (width1 > 0 && col1 >= 0 && col1 + n1 <= ld)), "row_rinv: bad second range");
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "row_rinv: unknown dtype %d", dtype);
+    if (T == 0) return 0;
+    const int threads = n0 + n1 >= 1024 ? 256 : 128;
+    cudaError_t e;
+    if (dtype == LI_F32)
+        e = li_launch_pdl(row_rinv_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)x, ld, col0, n0, width0, col1, n1, width1, eps, out);
+    else
+        e = li_launch_pdl(row_rinv_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)x, ld, col0, n0, width0, col1, n1, width1, eps, out);
+    if (e != cudaSuccess) return li_fail("row_rinv: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("row_rinv");
+}
 
 // proj, out: [T, (nh + 2 nkv) dh] in the run dtype (out may not be proj when taps > 1: tokens read their neighbours' rows).
 // conv_w [(nh + 2 nkv) dh, taps] float (NULL: no convolution; one tap: a factor per channel, no state); state [slots, state_stride] float with the
 // convolution's rows at state_off; q_norm, k_norm [dh] float (NULL: no norm), the mean of squares over norm_width
 // elements (dh, or fewer when heads are padded with zeros); rotary_dim 0: no rotation.  write 0: only q is made.
 // to_cache 0: keys and values go to their columns of `out` instead of the cache (li_rope_kv_write with rotary_dim 0 stores them).
+// row_rinv [T, 2] (may be NULL): the norm is over the whole projection of q and of k (li_row_rinv made the factors), and
+// q_norm [nh dh], k_norm [nkv dh] are weights per channel.  nkv 0 (write 0): proj holds queries only.  out_ld: elements
+// of a row of out (0: as many as proj's), so that queries alone can be written into rows that attention reads as q|k|v.
 // shift: the caller promises that every sequence of the step has one token; the state then moves on in this launch
 // (with write 0 it does not move at all: the entry that writes the cache moves it).
 LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* conv_w, int taps, float* state,
                                    long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
-                                   const float* q_norm, const float* k_norm, float eps, int norm_width, const int* positions, const float* denom,
-                                   int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh,
-                                   int page_size, int num_pages, int write, int shift, int to_cache, cudaStream_t stream) {
-    LI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && dh > 0 && page_size > 0, "conv_norm_rope_kv: bad sizes");
+                                   const float* q_norm, const float* k_norm, float eps, int norm_width, const float* row_rinv,
+                                   const int* positions, const float* denom, int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh,
+                                   int page_size, int num_pages, int write, int shift, int to_cache, int out_ld, cudaStream_t stream) {
+    if (out_ld == 0) out_ld = (nh + 2 * nkv) * dh;
+    LI_REQUIRE(out_ld >= (nh + 2 * nkv) * dh, "conv_norm_rope_kv: output rows of %d elements are too short", out_ld);
+    LI_REQUIRE(T >= 0 && nh > 0 && nkv >= 0 && dh > 0 && page_size > 0, "conv_norm_rope_kv: bad sizes");
+    LI_REQUIRE(nkv > 0 || !write, "conv_norm_rope_kv: keys and values are to be written, and there are none");
     LI_REQUIRE(dh <= 32 * kPerLane, "conv_norm_rope_kv: head_dim %d is larger than %d", dh, 32 * kPerLane);
     LI_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= dh, "conv_norm_rope_kv: rotary_dim %d must be even and at most head_dim %d",
                rotary_dim, dh);
     LI_REQUIRE(rotary_dim == 0 || denom != nullptr, "conv_norm_rope_kv: rotary_dim %d without denominators", rotary_dim);
     LI_REQUIRE(taps >= 1 && (taps == 1 || (conv_w != nullptr && state != nullptr && proj != out)),
                "conv_norm_rope_kv: a convolution over %d taps needs weights, a state and an output of its own", taps);
-    LI_REQUIRE((q_norm == nullptr) == (k_norm == nullptr), "conv_norm_rope_kv: queries and keys are normalised together or not at all");
+    LI_REQUIRE((q_norm == nullptr) == (k_norm == nullptr) || nkv == 0, "conv_norm_rope_kv: queries and keys are normalised together or not at all");
+    LI_REQUIRE(row_rinv == nullptr || q_norm != nullptr, "conv_norm_rope_kv: a norm over the whole projection needs its weights");
     LI_REQUIRE(norm_width > 0 && norm_width <= dh, "conv_norm_rope_kv: bad norm width %d", norm_width);
     LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "conv_norm_rope_kv: unknown dtype %d", dtype);
     if (T == 0) return 0;
@@ -178,8 +238,8 @@ LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const
     cudaError_t e;
 #define LI_CONV_LAUNCH(TT, TAPS_)                                                                                                             \
     e = li_launch_pdl(dh <= 128 ? conv_norm_rope_kv_kernel<TT, TAPS_, 4> : conv_norm_rope_kv_kernel<TT, TAPS_, kPerLane>, grid, dim3(kWarps * 32), smem, stream, (const TT*)proj, (TT*)out, conv_w, taps, state, \
-                      state_stride, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions, denom, rotary_dim,      \
-                      slot_mapping, (TT*)kcache, (TT*)vcache, (int)total, nh, nkv, dh, page_size, num_pages, write, (shift && write) ? 1 : 0, to_cache)
+                      state_stride, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, row_rinv, positions, denom, rotary_dim, \
+                      slot_mapping, (TT*)kcache, (TT*)vcache, (int)total, nh, nkv, dh, page_size, num_pages, write, (shift && write) ? 1 : 0, to_cache, out_ld)
 #define LI_CONV_TAPS(TT)                         \
     switch (conv_w ? taps : 1) {                 \
         case 1: LI_CONV_LAUNCH(TT, 1); break;    \

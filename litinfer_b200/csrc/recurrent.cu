@@ -13,8 +13,12 @@
 //     dt = softplus(dt_raw + dt_bias) per token and head, B and C shared by the heads of a group.
 //   * li_decay_scan: per head a state S [d, dv]:  S = decay S + k v^T,  o = S^T q, with q, k, v passed through
 //     x / (1 + exp(-x)) on the way in.
+//   * li_gla_scan: per head a state S [d, dv] with a decay per token and key channel:  S = diag(a_t) S + k v^T,
+//     o = S^T (q / sqrt(d)),  a_t = sigmoid(z_t)^(1 / tau) from float logits z.
+//   * li_channel_scan: a state S [N] per channel c with a decay per token, channel and element:
+//     S = exp(dt_c A[c, :]) S + dt_c x_c B,  y_c = (S . C + D_c x_c) silu(z_c),  dt = softplus(dt_raw), A = -exp(A_log).
 //   * li_gated_rmsnorm: RMSNorm in equal groups of a float row, with a gate before the norm (y * silu(z)) or after
-//     it (norm(y) * sigmoid(g)).
+//     it (norm(y) * sigmoid(g), or norm(y) * silu(g)).
 #include "common.cuh"
 
 namespace {
@@ -339,12 +343,221 @@ decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, i
     }
 }
 
+// Linear attention with a decay per token and key channel.  q, k [T, stride] at columns q_off + h d, k_off + h d; v at
+// v_off + h dv (no activation); za [T, za_stride] float: the decays' logits at za_off + h d.  a = exp(log sigmoid(z) / tau),
+// taken in float while staging; q is multiplied by q_scale there.  Columns, stages and passes as in decay_scan_kernel; the
+// chunk's decay is a number per key channel (the product of its tokens' decays, summed as logarithms).
+template <typename T, int E>
+__global__ void __launch_bounds__(512)
+gla_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int v_off, const float* __restrict__ za, int za_stride, int za_off,
+                float inv_tau, float q_scale, float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
+                const int* __restrict__ slots, float* __restrict__ out, int heads, int d, int dv, const int* __restrict__ seg, int mode,
+                float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
+    constexpr int DP = 32 * E;
+    const int warps = blockDim.x >> 5, cols = kWarpCols * warps;
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;                           // [kStage][DP]
+    float* ks = qs + kStage * DP;               // [kStage][DP]
+    float* as = ks + kStage * DP;               // [kStage][DP] decays
+    float* vs = as + kStage * DP;               // [kStage][cols]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y;
+    const Piece pc = piece_of(seg, q_start, slots);
+    const int q0 = pc.q0, q1 = pc.q1;
+    if (q1 <= q0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col0 = blockIdx.x * cols + warp * kWarpCols;
+    const size_t head_at = (size_t)h * dv * d;
+    float* st = state + (size_t)pc.slot * state_stride + head_at;
+    float* cst = chunk_state ? chunk_state + (size_t)pc.chunk * heads * dv * d + head_at : nullptr;
+    const float* from = mode == kScanWhole ? st : cst;
+    float S[kWarpCols][E];
+#pragma unroll
+    for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+            S[j][e] = (mode != kScanLocal && col0 + j < dv && E * lane + e < d) ? from[(size_t)(col0 + j) * d + E * lane + e] : 0.0f;
+    if (mode == kScanLocal && blockIdx.x == 0) {
+        // the chunk's decay per key channel, for the pass that carries states from chunk to chunk: the logarithms are summed
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float sum = 0.0f;
+            for (int t = q0; t < q1; ++t) sum += -softplus_f(-za[(size_t)t * za_stride + za_off + h * d + i]) * inv_tau;
+            chunk_decay[((size_t)pc.chunk * heads + h) * d + i] = expf(sum);
+        }
+    }
+    for (int t0 = q0; t0 < q1; t0 += kStage) {
+        const int nt = min(kStage, q1 - t0);
+        __syncthreads();
+        for (int tk = warp; tk < nt; tk += warps) {
+            const T* row = qkv + (size_t)(t0 + tk) * stride;
+            const float* zrow = za + (size_t)(t0 + tk) * za_stride + za_off + h * d;
+            for (int i = lane; i < DP; i += 32) {
+                if (mode != kScanLocal) qs[tk * DP + i] = i < d ? to_float(row[q_off + h * d + i]) * q_scale : 0.0f;
+                ks[tk * DP + i] = i < d ? to_float(row[k_off + h * d + i]) : 0.0f;
+                as[tk * DP + i] = i < d ? expf(-softplus_f(-zrow[i]) * inv_tau) : 0.0f;
+            }
+        }
+        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+            const int tk = e / cols, j = e - tk * cols;
+            const int c = blockIdx.x * cols + j;
+            vs[e] = c < dv ? to_float(qkv[(size_t)(t0 + tk) * stride + v_off + h * dv + c]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 2
+        for (int tk = 0; tk < nt; ++tk) {
+            float kk[E], aa[E], v[kWarpCols];
+            load_elements<E>(kk, ks + tk * DP + E * lane);
+            load_elements<E>(aa, as + tk * DP + E * lane);
+            load_elements<kWarpCols>(v, vs + tk * cols + warp * kWarpCols);
+            if (mode == kScanLocal) {
+#pragma unroll
+                for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+                    for (int e = 0; e < E; ++e) S[j][e] = fmaf(aa[e], S[j][e], kk[e] * v[j]);
+                continue;
+            }
+            float qq[E], acc[kWarpCols];
+            load_elements<E>(qq, qs + tk * DP + E * lane);
+#pragma unroll
+            for (int j = 0; j < kWarpCols; ++j) {
+                acc[j] = 0.0f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    S[j][e] = fmaf(aa[e], S[j][e], kk[e] * v[j]);
+                    acc[j] = fmaf(S[j][e], qq[e], acc[j]);
+                }
+            }
+            const float total = sum8_across_warp(acc, lane);
+            const int j = column_after_sum8(lane);
+            if ((lane & 3) == 0 && col0 + j < dv) out[(size_t)(t0 + tk) * heads * dv + h * dv + col0 + j] = total;
+        }
+    }
+    if (mode != kScanApply) {
+        float* to = mode == kScanWhole ? st : cst;
+#pragma unroll
+        for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+                if (col0 + j < dv && E * lane + e < d) to[(size_t)(col0 + j) * d + E * lane + e] = S[j][e];
+    }
+}
+
+// The selective scan with a state row per channel.  x [T, x_stride] at column x_off (after its convolution and activation),
+// bc [T, bc_stride]: B at column b_off, C at c_off (N each, shared by all channels), dt_raw [T, dt_stride] float (before the
+// softplus), z [T, z_stride] at z_off: the gate.  A channel is a column of the walk: a warp holds eight channels, each lane
+// E neighbouring state elements of all eight, and the channels' rates -exp(A_log) log2(e), so that a decay is one exp2.
+// The chunk's decay of channel c and element n is exp2(rate[c, n] * the sum of the chunk's step sizes of c).
+template <typename T, int E>
+__global__ void __launch_bounds__(512)
+channel_scan_kernel(const T* __restrict__ x, int x_stride, int x_off, const T* __restrict__ bc, int bc_stride, int b_off, int c_off,
+                    const float* __restrict__ dt_raw, int dt_stride, const T* __restrict__ z, int z_stride, int z_off,
+                    const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ state, long long state_stride,
+                    const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ y, int inner, int N,
+                    const int* __restrict__ seg, int mode, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
+    constexpr int NP = 32 * E;
+    const int warps = blockDim.x >> 5, cols = kWarpCols * warps;
+    extern __shared__ __align__(16) float smem[];
+    float* Bs = smem;                           // [kStage][NP]
+    float* Cs = Bs + kStage * NP;               // [kStage][NP]
+    float* xs = Cs + kStage * NP;               // [kStage][cols]
+    float* dts = xs + kStage * cols;            // [kStage][cols] step sizes
+    pdl_launch_dependents();
+    pdl_wait();
+    const Piece pc = piece_of(seg, q_start, slots);
+    const int q0 = pc.q0, q1 = pc.q1;
+    if (q1 <= q0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col0 = blockIdx.x * cols + warp * kWarpCols;          // this warp's first channel
+    float* st = state + (size_t)pc.slot * state_stride;
+    float* cst = chunk_state ? chunk_state + (size_t)pc.chunk * inner * N : nullptr;
+    const float* from = mode == kScanWhole ? st : cst;
+    float S[kWarpCols][E], rate[kWarpCols][E], dtsum[kWarpCols];
+#pragma unroll
+    for (int j = 0; j < kWarpCols; ++j) {
+        dtsum[j] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const bool in = col0 + j < inner && E * lane + e < N;
+            const size_t at = (size_t)(col0 + j) * N + E * lane + e;
+            S[j][e] = (mode != kScanLocal && in) ? from[at] : 0.0f;
+            rate[j][e] = in ? -expf(A_log[at]) * 1.4426950408889634f : 0.0f;
+        }
+    }
+    for (int t0 = q0; t0 < q1; t0 += kStage) {
+        const int nt = min(kStage, q1 - t0);
+        __syncthreads();                                   // the stage before has been used up
+        for (int tk = warp; tk < nt; tk += warps) {
+            const T* row = bc + (size_t)(t0 + tk) * bc_stride;
+            for (int n = lane; n < NP; n += 32) {
+                Bs[tk * NP + n] = n < N ? to_float(row[b_off + n]) : 0.0f;
+                if (mode != kScanLocal) Cs[tk * NP + n] = n < N ? to_float(row[c_off + n]) : 0.0f;
+            }
+        }
+        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+            const int tk = e / cols, j = e - tk * cols;
+            const int c = blockIdx.x * cols + j;
+            xs[e] = c < inner ? to_float(x[(size_t)(t0 + tk) * x_stride + x_off + c]) : 0.0f;
+            dts[e] = c < inner ? softplus_f(dt_raw[(size_t)(t0 + tk) * dt_stride + c]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 2
+        for (int tk = 0; tk < nt; ++tk) {
+            float b[E], xv[kWarpCols], dt[kWarpCols];
+            load_elements<E>(b, Bs + tk * NP + E * lane);
+            load_elements<kWarpCols>(xv, xs + tk * cols + warp * kWarpCols);
+            load_elements<kWarpCols>(dt, dts + tk * cols + warp * kWarpCols);
+            if (mode == kScanLocal) {
+#pragma unroll
+                for (int j = 0; j < kWarpCols; ++j) {
+                    const float dx = dt[j] * xv[j];
+                    dtsum[j] += dt[j];
+#pragma unroll
+                    for (int e = 0; e < E; ++e) S[j][e] = fmaf(exp2f(dt[j] * rate[j][e]), S[j][e], b[e] * dx);
+                }
+                continue;
+            }
+            float cc[E], acc[kWarpCols];
+            load_elements<E>(cc, Cs + tk * NP + E * lane);
+#pragma unroll
+            for (int j = 0; j < kWarpCols; ++j) {
+                const float dx = dt[j] * xv[j];
+                acc[j] = 0.0f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    S[j][e] = fmaf(exp2f(dt[j] * rate[j][e]), S[j][e], b[e] * dx);
+                    acc[j] = fmaf(S[j][e], cc[e], acc[j]);
+                }
+            }
+            const float total = sum8_across_warp(acc, lane);
+            const int j = column_after_sum8(lane);
+            if ((lane & 3) == 0 && col0 + j < inner) {
+                const int c = col0 + j;
+                const float r = fmaf(D[c], xs[tk * cols + warp * kWarpCols + j], total);
+                y[(size_t)(t0 + tk) * inner + c] = from_float<T>(r * silu_f(to_float(z[(size_t)(t0 + tk) * z_stride + z_off + c])));
+            }
+        }
+    }
+    if (mode != kScanApply) {
+        float* to = mode == kScanWhole ? st : cst;
+#pragma unroll
+        for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+                if (col0 + j < inner && E * lane + e < N) {
+                    const size_t at = (size_t)(col0 + j) * N + E * lane + e;
+                    to[at] = S[j][e];
+                    if (mode == kScanLocal) chunk_decay[(size_t)pc.chunk * inner * N + at] = exp2f(dtsum[j] * rate[j][e]);
+                }
+    }
+}
+
 // Between the two passes over chunks: for each run of chunks (a sequence's, in order) S starts as the slot's state;
 // chunk_state[chunk] (the chunk's end state from zeros) is replaced by the state the chunk starts from, and
 // S <- decay[chunk, head] S + end state.  The last S goes back to the slot.
 __global__ void scan_carry_kernel(float* __restrict__ state, long long state_stride, float* __restrict__ chunk_state,
                                   const float* __restrict__ chunk_decay, const float* __restrict__ token_decay, const int* __restrict__ seg,
-                                  const int* __restrict__ runs, int heads, int per_head) {
+                                  const int* __restrict__ runs, int heads, int per_head, int period) {
     pdl_launch_dependents();
     pdl_wait();
     const int first = runs[3 * blockIdx.y], count = runs[3 * blockIdx.y + 1], slot = runs[3 * blockIdx.y + 2];
@@ -352,6 +565,9 @@ __global__ void scan_carry_kernel(float* __restrict__ state, long long state_str
     const int elements = heads * per_head;
     if (e >= elements) return;
     const int h = e / per_head;
+    // a decay per chunk and head (period 0), or `period` of them per head: element i of a head takes number i % period
+    const int per_chunk = period > 0 ? heads * period : heads;
+    const int dec_at = period > 0 ? h * period + (e - h * per_head) % period : h;
     float* st = state + (size_t)slot * state_stride + e;
     float S = *st;
     for (int c0 = first; c0 < first + count; c0 += 8) {
@@ -363,7 +579,7 @@ __global__ void scan_carry_kernel(float* __restrict__ state, long long state_str
             const bool in = c < first + count;
             z[u] = in ? chunk_state[(size_t)c * elements + e] : 0.0f;
             // the chunk's decay: given, or a constant per token and head to the power of the chunk's length
-            dec[u] = !in ? 1.0f : chunk_decay ? chunk_decay[(size_t)c * heads + h] : powf(token_decay[h], (float)(seg[4 * c + 1] - seg[4 * c]));
+            dec[u] = !in ? 1.0f : chunk_decay ? chunk_decay[(size_t)c * per_chunk + dec_at] : powf(token_decay[h], (float)(seg[4 * c + 1] - seg[4 * c]));
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -376,7 +592,7 @@ __global__ void scan_carry_kernel(float* __restrict__ state, long long state_str
     *st = S;
 }
 
-// One block per (token, group).  mode 0: v = y silu(z), out = v rinv w; mode 1: out = y rinv w sigmoid(z).
+// One block per (token, group).  mode 0: v = y silu(z), out = v rinv w; mode 1: out = y rinv w sigmoid(z); mode 2: out = y rinv w silu(z).
 template <typename T>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride, int gate_off, const float* __restrict__ w,
                                      float eps, int mode, T* __restrict__ out, int n, int groups) {
@@ -400,7 +616,8 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const T* __res
         float v = yr[j];
         const float z = to_float(zr[j]);
         if (mode == 0) v = (v * silu_f(z)) * rinv * w[g * gs + j];
-        else v = (v * rinv * w[g * gs + j]) * sigmoid_f(z);
+        else if (mode == 1) v = (v * rinv * w[g * gs + j]) * sigmoid_f(z);
+        else v = (v * rinv * w[g * gs + j]) * silu_f(z);
         o[j] = from_float<T>(v);
     }
 }
@@ -527,16 +744,97 @@ LI_EXPORT int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, i
 #undef LI_SCAN
 }
 
+template <typename T, int E>
+static int launch_gla(const void* qkv, int stride, int q_off, int k_off, int v_off, const float* za, int za_stride, int za_off, float inv_tau,
+                      float q_scale, float* state, long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads,
+                      int d, int dv, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
+    const int warps = scan_warps(dv), cols = warps * kWarpCols;
+    const size_t smem = ((size_t)3 * kStage * 32 * E + kStage * cols) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(gla_scan_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(gla_scan_kernel<T, E>, dim3(ceil_div(dv, cols), heads, S), dim3(warps * 32), smem, stream, (const T*)qkv, stride,
+                                  q_off, k_off, v_off, za, za_stride, za_off, inv_tau, q_scale, state, state_stride, q_start, slots, out, heads, d, dv,
+                                  seg, mode, chunk_state, chunk_decay);
+    if (e != cudaSuccess) return li_fail("gla_scan: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("gla_scan");
+}
+
+// The state of a slot: [heads][dv][d] (a column of the head's d x dv matrix at a time).  chunk_decay: [chunks, heads, d].
+LI_EXPORT int li_gla_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const float* za, int za_stride, int za_off,
+                          float inv_tau, float q_scale, float* state, long long state_stride, const int* q_start, const int* slots, float* out,
+                          int S, int heads, int d, int dv, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
+    LI_REQUIRE(mode == kScanWhole ? seg == nullptr : (seg != nullptr && chunk_state != nullptr && chunk_decay != nullptr && (uintptr_t)seg % 16 == 0),
+               "gated linear attention: pass %d needs the chunks, their states and their decays (or none of them)", mode);
+    LI_REQUIRE(heads > 0 && d > 0 && d <= 256 && dv > 0, "gated linear attention: %d heads of %d x %d (keys of at most 256)", heads, d, dv);
+    LI_REQUIRE(za != nullptr && za_off >= 0 && za_off + heads * d <= za_stride, "gated linear attention: decays at column %d of %d", za_off, za_stride);
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "gated linear attention: unknown dtype %d", dtype);
+    if (S == 0) return 0;
+    LI_REQUIRE(S <= 65535 && heads <= 65535, "gated linear attention: %d sequences or %d heads in one launch", S, heads);
+#define LI_SCAN(RR)                                                                                                                              \
+    return dtype == LI_F32 ? launch_gla<float, RR>(qkv, stride, q_off, k_off, v_off, za, za_stride, za_off, inv_tau, q_scale, state, state_stride,  \
+                                                   q_start, slots, out, S, heads, d, dv, seg, mode, chunk_state, chunk_decay, stream)           \
+                           : launch_gla<bf16, RR>(qkv, stride, q_off, k_off, v_off, za, za_stride, za_off, inv_tau, q_scale, state, state_stride,   \
+                                                  q_start, slots, out, S, heads, d, dv, seg, mode, chunk_state, chunk_decay, stream)
+    if (d <= 32) { LI_SCAN(1); }
+    if (d <= 64) { LI_SCAN(2); }
+    if (d <= 128) { LI_SCAN(4); }
+    LI_SCAN(8);
+#undef LI_SCAN
+}
+
+template <typename T, int E>
+static int launch_channel(const void* x, int x_stride, int x_off, const void* bc, int bc_stride, int b_off, int c_off, const float* dt_raw,
+                          int dt_stride, const void* z, int z_stride, int z_off, const float* A_log, const float* D, float* state,
+                          long long state_stride, const int* q_start, const int* slots, void* y, int S, int inner, int N, const int* seg, int mode,
+                          float* chunk_state, float* chunk_decay, cudaStream_t stream) {
+    const int warps = scan_warps(inner) > 8 ? 8 : scan_warps(inner), cols = warps * kWarpCols;
+    const size_t smem = ((size_t)2 * kStage * 32 * E + 2 * kStage * cols) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(channel_scan_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(channel_scan_kernel<T, E>, dim3(ceil_div(inner, cols), 1, S), dim3(warps * 32), smem, stream, (const T*)x, x_stride,
+                                  x_off, (const T*)bc, bc_stride, b_off, c_off, dt_raw, dt_stride, (const T*)z, z_stride, z_off, A_log, D, state,
+                                  state_stride, q_start, slots, (T*)y, inner, N, seg, mode, chunk_state, chunk_decay);
+    if (e != cudaSuccess) return li_fail("channel_scan: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("channel_scan");
+}
+
+// The state of a slot: [inner][N].  chunk_decay: [chunks, inner, N].
+LI_EXPORT int li_channel_scan(const void* x, int dtype, int x_stride, int x_off, const void* bc, int bc_stride, int b_off, int c_off,
+                              const float* dt_raw, int dt_stride, const void* z, int z_stride, int z_off, const float* A_log, const float* D,
+                              float* state, long long state_stride, const int* q_start, const int* slots, void* y, int S, int inner, int N,
+                              const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
+    LI_REQUIRE(mode == kScanWhole ? seg == nullptr : (seg != nullptr && chunk_state != nullptr && chunk_decay != nullptr && (uintptr_t)seg % 16 == 0),
+               "channel scan: pass %d needs the chunks, their states and their decays (or none of them)", mode);
+    LI_REQUIRE(inner > 0 && N > 0 && N <= 256, "channel scan: %d channels with a state of %d (at most 256)", inner, N);
+    LI_REQUIRE(x_off >= 0 && x_off + inner <= x_stride && z_off >= 0 && z_off + inner <= z_stride && inner <= dt_stride && b_off >= 0 &&
+                   b_off + N <= bc_stride && c_off >= 0 && c_off + N <= bc_stride, "channel scan: columns outside their rows");
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "channel scan: unknown dtype %d", dtype);
+    if (S == 0) return 0;
+    LI_REQUIRE(S <= 65535, "channel scan: %d sequences in one launch", S);
+#define LI_SCAN(RR)                                                                                                                               \
+    return dtype == LI_F32 ? launch_channel<float, RR>(x, x_stride, x_off, bc, bc_stride, b_off, c_off, dt_raw, dt_stride, z, z_stride, z_off, A_log, \
+                                                       D, state, state_stride, q_start, slots, y, S, inner, N, seg, mode, chunk_state, chunk_decay, \
+                                                       stream)                                                                                   \
+                           : launch_channel<bf16, RR>(x, x_stride, x_off, bc, bc_stride, b_off, c_off, dt_raw, dt_stride, z, z_stride, z_off, A_log,  \
+                                                      D, state, state_stride, q_start, slots, y, S, inner, N, seg, mode, chunk_state, chunk_decay,  \
+                                                      stream)
+    if (N <= 32) { LI_SCAN(1); }
+    if (N <= 64) { LI_SCAN(2); }
+    if (N <= 128) { LI_SCAN(4); }
+    LI_SCAN(8);
+#undef LI_SCAN
+}
+
 // See scan_carry_kernel.  runs: triples (first chunk, chunks, slot); per_head: state elements of one head.  The decay of a
-// chunk and head: chunk_decay[chunk, head], or (chunk_decay null) token_decay[head] to the power of the chunk's length.
+// chunk and head: chunk_decay[chunk, head], or (chunk_decay null) token_decay[head] to the power of the chunk's length; with
+// period > 0 chunk_decay is [chunk, head, period] and element i of a head's state decays by number i % period.
 LI_EXPORT int li_scan_carry(float* state, long long state_stride, float* chunk_state, const float* chunk_decay, const float* token_decay,
-                            const int* seg, const int* runs, int nruns, int heads, int per_head, cudaStream_t stream) {
+                            const int* seg, const int* runs, int nruns, int heads, int per_head, int period, cudaStream_t stream) {
     LI_REQUIRE(heads > 0 && per_head > 0, "scan carry: %d heads of %d elements", heads, per_head);
+    LI_REQUIRE(period >= 0 && (period == 0 || (chunk_decay != nullptr && per_head % period == 0)), "scan carry: %d decays a head for %d elements", period, per_head);
     LI_REQUIRE(chunk_decay != nullptr || (token_decay != nullptr && seg != nullptr), "scan carry: no decay given");
     if (nruns == 0) return 0;
     LI_REQUIRE(nruns <= 65535, "scan carry: %d sequences in one launch", nruns);
     cudaError_t e = li_launch_pdl(scan_carry_kernel, dim3(ceil_div(heads * per_head, 256), nruns), dim3(256), 0, stream, state, state_stride, chunk_state,
-                                  chunk_decay, token_decay, seg, runs, heads, per_head);
+                                  chunk_decay, token_decay, seg, runs, heads, per_head, period);
     if (e != cudaSuccess) return li_fail("scan_carry: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("scan_carry");
 }
@@ -544,7 +842,7 @@ LI_EXPORT int li_scan_carry(float* state, long long state_stride, float* chunk_s
 LI_EXPORT int li_gated_rmsnorm(const float* y, const void* gate, int dtype, int gate_stride, int gate_off, const float* w, float eps, int mode,
                                void* out, int T, int n, int groups, cudaStream_t stream) {
     LI_REQUIRE(n > 0 && groups > 0 && n % groups == 0, "gated norm: %d columns in %d groups", n, groups);
-    LI_REQUIRE(mode == 0 || mode == 1, "gated norm: unknown mode %d", mode);
+    LI_REQUIRE(mode >= 0 && mode <= 2, "gated norm: unknown mode %d", mode);
     LI_REQUIRE(gate_off >= 0 && gate_off + n <= gate_stride, "gated norm: gate at column %d of %d for %d columns", gate_off, gate_stride, n);
     if (T == 0) return 0;
     const long long blocks = (long long)T * groups;

@@ -90,6 +90,7 @@ class ModelRunner:
         # ... except decode steps, if every such mixer says that it takes them from the device's copy of the step
         # (parts.base.Mixer.decodes_from_device); the warm-up runs of a capture then go to the spare slot
         stateful = [m for b in model.blocks for m in mixers_with_state(b)]
+        stateful += [p for p in getattr(model, "stream_inputs", []) if has_fixed_state(p.cache_requirement())]
         self._state_in_graphs = bool(stateful) and all(getattr(m, "decodes_from_device", False) for m in stateful)
         # the block tables stay on the device (manager.groups[g].tables); a step uploads what changed
         self.resident = bool(manager.groups) and all(g.tables is not None for g in manager.groups) and os.environ.get("LITINFER_B200_RESIDENT_TABLES", "1") != "0"

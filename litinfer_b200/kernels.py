@@ -109,6 +109,28 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out32: torch.Tensor) -> No
     _check(library().li_embedding(_p(table), _i(_dt(table)), _p(ids), _p(out32), _i(T), _i(H), _i(V), _stream(out32)), "embedding")
 
 
+def add_pair_rows(x32: torch.Tensor, pairs: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, q_start: torch.Tensor,
+                  seq_of_token: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, mul_prev: int, mul_cur: int) -> None:
+    """``x32[t] += pairs[(prev * mul_prev + ids[t] * mul_cur) mod buckets]`` with ``prev`` the token before ``t`` in its
+    sequence: the one before it in the step, or, for the first token of a portion, the sequence's last token of the step
+    before, kept in ``state[slot, 0]`` (int32); a sequence's first token (position 0) takes row ``buckets``, the table's
+    last.  The state moves on to the portion's last token in the same launch."""
+    T, H = x32.shape
+    _need(x32, "residual stream", torch.float32)
+    _need(pairs, "table of pairs", None, (pairs.shape[0], H))
+    _need(ids, "token ids", torch.int32)
+    _need(positions, "positions", torch.int32, (T,))
+    _need(q_start, "q_start", torch.int32)
+    _need(seq_of_token, "seq_of_token", torch.int32, (T,))
+    _need(slots, "state slots", torch.int32)
+    _need(state, "state of previous tokens", torch.int32)
+    if state.dim() != 2 or pairs.shape[0] < 2:
+        raise KernelError(f"add_pair_rows: state {tuple(state.shape)}, table {tuple(pairs.shape)}")
+    _check(library().li_add_pair_rows(_p(x32), _p(pairs), _i(_dt(pairs)), _p(ids), _p(positions), _p(q_start), _p(seq_of_token), _p(slots),
+                                      _p(state), _l(state.shape[1]), _i(pairs.shape[0] - 1), _l(int(mul_prev)), _l(int(mul_cur)), _i(T), _i(H),
+                                      _stream(x32)), "add_pair_rows")
+
+
 def rmsnorm(x32: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
     T, H = x32.shape
     _need(x32, "rmsnorm input", torch.float32)
@@ -694,7 +716,7 @@ def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.
     cstate, cdecay = _scan_passes(chunks, heads * head_dim * state_size, heads, xbc.device)
     run(chunks.seg, chunks.count, 1, cstate, cdecay)
     _check(library().li_scan_carry(st, stride, _p(cstate), _p(cdecay), _p(None), _p(chunks.seg), _p(chunks.runs), _i(chunks.nruns), _i(heads),
-                                   _i(head_dim * state_size), _stream(y32)), "scan_carry")
+                                   _i(head_dim * state_size), _i(0), _stream(y32)), "scan_carry")
     run(chunks.seg, chunks.count, 2, cstate, cdecay)
 
 
@@ -724,22 +746,94 @@ def decay_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: tor
     cstate = torch.empty((chunks.count, heads * dim * vdim), dtype=torch.float32, device=qkv.device)
     run(chunks.seg, chunks.count, 1, cstate)
     _check(library().li_scan_carry(st, stride, _p(cstate), _p(None), _p(decay), _p(chunks.seg), _p(chunks.runs), _i(chunks.nruns), _i(heads),
-                                   _i(dim * vdim), _stream(out32)), "scan_carry")
+                                   _i(dim * vdim), _i(0), _stream(out32)), "scan_carry")
     run(chunks.seg, chunks.count, 2, cstate)
 
 
+def gla_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, za: torch.Tensor, za_col: int, tau: float, state: torch.Tensor,
+             q_start: torch.Tensor, slots: torch.Tensor, out32: torch.Tensor, heads: int, dim: int, vdim: int,
+             chunks: Optional[ScanChunks] = None) -> None:
+    """Linear attention with a decay per token and key channel, state ``S [dim, vdim]`` per head at the start of
+    ``state[slot]``: ``S = diag(a_t) S + k_t v_t^T``; ``out_t = S^T q_t / sqrt(dim)``; ``a_t = sigmoid(z_t)^(1 / tau)`` with
+    the float32 logits z in the ``heads * dim`` columns of ``za`` from ``za_col``; q, k, v are the columns of ``qkv`` at
+    ``q_col``, ``k_col``, ``v_col`` as they are.  The state is kept column by column, ``[heads, vdim, dim]``.
+    ``chunks``: as in :func:`ssm_scan`; a chunk's decay is a number per head and key channel."""
+    T = qkv.shape[0]
+    _need(qkv, "q|k|v")
+    _need(za, "decay logits", torch.float32)
+    _need(out32, "scan output", torch.float32, (T, heads * vdim))
+    S = q_start.shape[0] - 1
+    _need(slots, "state slots", torch.int32, (S,))
+    st, stride, _ = _state_args(state, 0)
+    if heads * dim * vdim > state.shape[1] or za.shape[0] != T:
+        raise KernelError("gla_scan: the state or the decays are too small")
+
+    def run(seg, n, mode, cstate, cdecay):
+        _check(library().li_gla_scan(_p(qkv), _i(_dt(qkv)), _i(qkv.shape[1]), _i(q_col), _i(k_col), _i(v_col), _p(za), _i(za.shape[1]), _i(za_col),
+                                     _f(1.0 / float(tau)), _f(float(dim) ** -0.5), st, stride, _p(q_start), _p(slots), _p(out32), _i(n), _i(heads),
+                                     _i(dim), _i(vdim), _p(seg), _i(mode), _p(cstate), _p(cdecay), _stream(out32)), "gla_scan")
+
+    if chunks is None or chunks.count == 0:
+        return run(None, S, 0, None, None)
+    cstate = torch.empty((chunks.count, heads * dim * vdim), dtype=torch.float32, device=qkv.device)
+    cdecay = torch.empty((chunks.count, heads * dim), dtype=torch.float32, device=qkv.device)
+    run(chunks.seg, chunks.count, 1, cstate, cdecay)
+    _check(library().li_scan_carry(st, stride, _p(cstate), _p(cdecay), _p(None), _p(chunks.seg), _p(chunks.runs), _i(chunks.nruns), _i(heads),
+                                   _i(dim * vdim), _i(dim), _stream(out32)), "scan_carry")
+    run(chunks.seg, chunks.count, 2, cstate, cdecay)
+
+
+def channel_scan(x: torch.Tensor, x_col: int, bc: torch.Tensor, b_col: int, c_col: int, dt32: torch.Tensor, z: torch.Tensor, z_col: int,
+                 A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, y: torch.Tensor,
+                 chunks: Optional[ScanChunks] = None) -> None:
+    """The selective scan with a state row per channel, ``S [inner, N]`` at the start of ``state[slot]``:
+    ``dt = softplus(dt32[t])`` (float32, one per channel); ``S[c] = exp(-exp(A_log[c]) dt_c) S[c] + dt_c x_c B_t``;
+    ``y[t, c] = (S[c] . C_t + D[c] x_c) silu(z_c)``.  x: the ``inner`` columns of ``x`` from ``x_col``; B and C: N columns of
+    ``bc`` from ``b_col`` and ``c_col``; z: the columns of ``z`` from ``z_col``; y in the run dtype.  ``chunks``: as in
+    :func:`ssm_scan`; a chunk's decay is a number per element of the state."""
+    T = x.shape[0]
+    inner, N = A_log.shape
+    _need(x, "scan input")
+    _need(bc, "B|C", x.dtype)
+    _need(z, "gate", x.dtype)
+    _need(dt32, "step sizes", torch.float32, (T, inner))
+    _need(A_log, "A_log", torch.float32)
+    _need(D, "D", torch.float32, (inner,))
+    _need(y, "scan output", x.dtype, (T, inner))
+    S = q_start.shape[0] - 1
+    _need(slots, "state slots", torch.int32, (S,))
+    st, stride, _ = _state_args(state, 0)
+    if inner * N > state.shape[1] or bc.shape[0] != T or z.shape[0] != T:
+        raise KernelError("channel_scan: the state or an input is too small")
+
+    def run(seg, n, mode, cstate, cdecay):
+        _check(library().li_channel_scan(_p(x), _i(_dt(x)), _i(x.shape[1]), _i(x_col), _p(bc), _i(bc.shape[1]), _i(b_col), _i(c_col), _p(dt32),
+                                         _i(dt32.shape[1]), _p(z), _i(z.shape[1]), _i(z_col), _p(A_log), _p(D), st, stride, _p(q_start), _p(slots),
+                                         _p(y), _i(n), _i(inner), _i(N), _p(seg), _i(mode), _p(cstate), _p(cdecay), _stream(y)), "channel_scan")
+
+    if chunks is None or chunks.count == 0:
+        return run(None, S, 0, None, None)
+    cstate = torch.empty((chunks.count, inner * N), dtype=torch.float32, device=x.device)
+    cdecay = torch.empty((chunks.count, inner * N), dtype=torch.float32, device=x.device)
+    run(chunks.seg, chunks.count, 1, cstate, cdecay)
+    _check(library().li_scan_carry(st, stride, _p(cstate), _p(cdecay), _p(None), _p(chunks.seg), _p(chunks.runs), _i(chunks.nruns), _i(1),
+                                   _i(inner * N), _i(inner * N), _stream(y)), "scan_carry")
+    run(chunks.seg, chunks.count, 2, cstate, cdecay)
+
+
 def gated_rmsnorm(y32: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: torch.Tensor, eps: float, groups: int, gate_first: bool,
-                  out: torch.Tensor) -> None:
+                  out: torch.Tensor, gate_act: str = "sigmoid") -> None:
     """RMSNorm of ``y32`` [T, n] in ``groups`` equal parts, times ``weight``.  ``gate_first``: y is multiplied by
-    silu(gate) before the norm; otherwise the normalised result is multiplied by sigmoid(gate).  The gate is the n
-    columns of ``gate`` from ``gate_col``."""
+    silu(gate) before the norm; otherwise the normalised result is multiplied by sigmoid(gate) (``gate_act`` "silu": by
+    silu(gate)).  The gate is the n columns of ``gate`` from ``gate_col``."""
     T, n = y32.shape
     _need(y32, "norm input", torch.float32)
     _need(gate, "gate")
     _need(weight, "rmsnorm weight", torch.float32, (n,))
     _need(out, "norm output", gate.dtype, (T, n))
     _check(library().li_gated_rmsnorm(_p(y32), _p(gate), _i(_dt(gate)), _i(gate.shape[1]), _i(gate_col), _p(weight), _f(eps),
-                                      _i(0 if gate_first else 1), _p(out), _i(T), _i(n), _i(groups), _stream(out)), "gated_rmsnorm")
+                                      _i(0 if gate_first else (2 if gate_act == "silu" else 1)), _p(out), _i(T), _i(n), _i(groups), _stream(out)),
+           "gated_rmsnorm")
 
 
 # --------------------------------------------------------------------------
@@ -767,7 +861,7 @@ def norm_add_norm(x32: torch.Tensor, y, post: Optional[tuple], nxt: Optional[tup
     """Per token: ``x32 += post(y)``, then ``out = nxt(x32)``.  A norm is a tuple ``(weight, centered, eps)``: centered takes
     the mean off and divides by the root of the variance (mean of squared deviations) + eps, not centered divides by the
     root of the mean of squares + eps; both multiply by the weight.  ``post`` None: ``x32 += y``; ``y`` None: nothing is
-    added; ``nxt`` None: no output.  ``rows`` (int32, only without ``y``): ``out[r] = nxt(x32[rows[r]])``.  ``y`` may be a
+    added; ``nxt`` None: no output; ``nxt`` with a weight of None: ``out`` is ``x32`` as it is, in the run dtype.  ``rows`` (int32, only without ``y``): ``out[r] = nxt(x32[rows[r]])``.  ``y`` may be a
     :class:`RowSum`: the sum is then taken inside this kernel, in float32."""
     n_src, H = x32.shape
     _need(x32, "residual stream", torch.float32)
@@ -795,10 +889,11 @@ def norm_add_norm(x32: torch.Tensor, y, post: Optional[tuple], nxt: Optional[tup
         _need(wp, "norm weight (after the sublayer)", torch.float32, (H,))
     if wn is not None:
         _need(wn, "norm weight (before the next sublayer)", torch.float32, (H,))
+    if nxt is not None:
         _need(out, "normalised output", y.dtype if y is not None else None, (R, H))
     dt = _dt(y) if y is not None else _dt(out)
     _check(library().li_norm_add_norm(_p(x32), _p(y), _i(dt), _p(wp), _i(1 if cp else 0), _f(ep), _p(wn), _i(1 if cn else 0), _f(en),
-                                      _p(out if wn is not None else None), _p(rows), _i(R), _i(n_src), _i(H), _p(places), _i(top), _p(y_weights),
+                                      _p(out if nxt is not None else None), _p(rows), _i(R), _i(n_src), _i(H), _p(places), _i(top), _p(y_weights),
                                       _stream(x32)), "norm_add_norm")
 
 
@@ -829,7 +924,7 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
                       k_norm: Optional[torch.Tensor], eps: float, norm_width: int, positions: torch.Tensor,
                       denominators: Optional[torch.Tensor], rotary_dim: int, slot_mapping: torch.Tensor, k_cache: torch.Tensor,
                       v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, write: bool = True, shift: bool = False,
-                      to_cache: bool = True) -> None:
+                      to_cache: bool = True, row_rinv: Optional[torch.Tensor] = None) -> None:
     """What stands between a q|k|v product ``proj`` [T, (heads + 2 kv_heads) head_dim] and attention: a causal convolution
     per channel over the last ``taps`` projected rows (``conv_w`` float32 [channels, taps], the last column the token's own;
     rows before a portion come from ``state[slot, state_off:]`` as [taps - 1, channels], oldest first; one tap is a factor
@@ -842,7 +937,9 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
     T = proj.shape[0]
     N = (num_heads + 2 * num_kv_heads) * head_dim
     _need(proj, "q|k|v projection", None, (T, N))
-    _need(out, "q|k|v output", proj.dtype, (T, N))
+    _need(out, "q|k|v output", proj.dtype)
+    if out.dim() != 2 or out.shape[0] != T or out.shape[1] < N:
+        raise KernelError(f"conv_norm_rope_kv: output of shape {tuple(out.shape)} for {T} rows of {N}")
     taps = 1
     if conv_w is not None:
         _need(conv_w, "convolution weight", torch.float32)
@@ -854,9 +951,11 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
         st, stride, off = _state_args(state, state_off)
         if state_off + (taps - 1) * N > state.shape[1]:
             raise KernelError("conv_norm_rope_kv: the state is too small for the convolution's inputs")
-    for t, n in ((q_norm, "query norm weight"), (k_norm, "key norm weight")):
+    for t, n, hh in ((q_norm, "query norm weight", num_heads), (k_norm, "key norm weight", num_kv_heads)):
         if t is not None:
-            _need(t, n, torch.float32, (head_dim,))
+            _need(t, n, torch.float32, (head_dim * hh,) if row_rinv is not None else (head_dim,))
+    if row_rinv is not None:
+        _need(row_rinv, "norm factors of the rows", torch.float32, (T, 2))
     _need(positions, "positions", torch.int32, (T,))
     if rotary_dim:
         _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
@@ -867,13 +966,30 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
     _need(k_cache, "key cache", proj.dtype)
     pages, nkv, page_size, dh = k_cache.shape
     _need(v_cache, "value cache", proj.dtype, (pages, nkv, dh, page_size))
-    if nkv != num_kv_heads or dh != head_dim:
+    if num_kv_heads == 0:
+        if write:
+            raise KernelError("conv_norm_rope_kv: a projection of queries alone writes no keys and values")
+    elif nkv != num_kv_heads or dh != head_dim:
         raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
     _check(library().li_conv_norm_rope_kv(
         _p(proj), _p(out), _i(_dt(proj)), _p(conv_w), _i(taps), st, stride, off, _p(q_start), _p(seq_of_token), _p(slots),
-        _p(q_norm), _p(k_norm), _f(eps), _i(int(norm_width)), _p(positions), _p(denominators if rotary_dim else None), _i(rotary_dim),
+        _p(q_norm), _p(k_norm), _f(eps), _i(int(norm_width)), _p(row_rinv), _p(positions), _p(denominators if rotary_dim else None), _i(rotary_dim),
         _p(slot_mapping), _p(k_cache), _p(v_cache), _i(T), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages),
-        _i(1 if write else 0), _i(1 if shift else 0), _i(1 if to_cache else 0), _stream(out)), "conv_norm_rope_kv")
+        _i(1 if write else 0), _i(1 if shift else 0), _i(1 if to_cache else 0), _i(out.shape[1]), _stream(out)), "conv_norm_rope_kv")
+
+
+def row_rinv(x: torch.Tensor, ranges, eps: float, out: torch.Tensor) -> None:
+    """``out[t, j] = 1 / sqrt(sum(x[t, col_j : col_j + n_j]^2) / width_j + eps)`` for one or two ``ranges`` (col, n, width):
+    the factor of an RMS norm over a whole projection (``width``: how many of the n columns are real, the rest zero padding)."""
+    T = x.shape[0]
+    _need(x, "rows")
+    _need(out, "norm factors", torch.float32, (T, 2))
+    r = [tuple(int(v) for v in rg) for rg in ranges]
+    if not 1 <= len(r) <= 2:
+        raise KernelError("row_rinv: one or two ranges of columns")
+    (c0, n0, w0), (c1, n1, w1) = r[0], (r[1] if len(r) == 2 else (0, 0, 1))
+    _check(library().li_row_rinv(_p(x), _i(_dt(x)), _i(x.shape[1]), _i(c0), _i(n0), _i(w0), _i(c1), _i(n1), _i(w1), _f(eps), _p(out), _i(T),
+                                 _stream(out)), "row_rinv")
 
 
 # --------------------------------------------------------------------------
@@ -920,14 +1036,18 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row
            "grouped_linear")
 
 
-def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, scoring: str = "sigmoid") -> None:
     """``ids``, ``weights`` [T, top]: per token the experts with the largest ``sigmoid(logits)`` (the lower index wins a tie)
-    and those scores."""
+    and those scores; ``scoring`` "softmax_chosen": the experts with the largest logits, and the softmax over the chosen
+    logits alone."""
+    if scoring not in ("sigmoid", "softmax_chosen"):
+        raise KernelError(f"moe_route: unknown scoring {scoring!r}")
     T, E = logits.shape
     _need(logits, "router logits", torch.float32)
     _need(ids, "expert ids", torch.int32, (T, top))
     _need(weights, "expert weights", torch.float32, (T, top))
-    _check(library().li_moe_route(_p(logits), _i(T), _i(E), _i(top), _p(ids), _p(weights), _stream(ids)), "moe_route")
+    _check(library().li_moe_route(_p(logits), _i(0 if scoring == "sigmoid" else 1), _i(T), _i(E), _i(top), _p(ids), _p(weights), _stream(ids)),
+           "moe_route")
 
 
 def sorted_rows(pairs: int, experts: int, pad: int = 1) -> int:

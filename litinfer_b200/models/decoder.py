@@ -21,7 +21,7 @@ import torch
 
 from .. import kernels as K
 from ..config import ModelSpec, load_config, validate_schedule
-from ..parts import BLOCKS, NORMS, POSITIONS
+from ..parts import BLOCKS, NORMS, POSITIONS, STREAM_INPUTS
 from ..parts.base import FixedState, PagedKV
 from ..weights.loader import ParamSpec, load_tensors
 from ..weights.random_init import random_tensors
@@ -53,6 +53,8 @@ class DecoderModel:
         self.final_norm = NORMS.build(spec.final_norm, spec.final_norm_prefix, self.dtype, self.device)
         self.position = (POSITIONS.build(spec.position, spec.position_prefix, self.dtype, self.device)
                          if spec.position is not None else None)
+        # what else joins the stream after the embedding (an embedding of token pairs); their caches come behind the schedule's
+        self.stream_inputs = [STREAM_INPUTS.build(p, prefix, self.dtype, self.device) for p, prefix in spec.stream_inputs]
         self.stream_tables: Dict[str, torch.Tensor] = {}      # vectors that schedule entries add to the stream (ScheduleEntry.add)
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
@@ -67,6 +69,8 @@ class DecoderModel:
         out = [ParamSpec(s.embedding_name, (s.vocab_size, s.hidden_size), role="matrix")]
         if self.position is not None:
             out.extend(self.position.all_params())
+        for part in self.stream_inputs:
+            out.extend(part.all_params())
         for name, rows in s.stream_tables.items():
             out.append(ParamSpec(name, (int(rows), s.hidden_size), role="vector", std=0.02))
         for b in self.blocks:
@@ -84,6 +88,8 @@ class DecoderModel:
         self.embedding = tensors.pop(s.embedding_name)
         if self.position is not None:
             self.position.bind_all(tensors)
+        for part in self.stream_inputs:
+            part.bind_all(tensors)
         self.stream_tables = {name: tensors.pop(name) for name in s.stream_tables}
         for b in self.blocks:
             b.bind_all(tensors)
@@ -97,10 +103,12 @@ class DecoderModel:
             raise RuntimeError("tensors left unbound: " + ", ".join(sorted(tensors)))
 
     def cache_requirements(self):
-        """For each schedule entry: PagedKV, FixedState or None (entries that read another's cache: None)."""
+        """For each schedule entry: PagedKV, FixedState or None (entries that read another's cache: None); behind them,
+        what the model's own stream inputs ask for, one each."""
         out = []
         for e in self.spec.schedule:
             out.append(self.blocks[e.block].cache_requirement() if e.cache_from is None else None)
+        out.extend(part.cache_requirement() for part in self.stream_inputs)
         return out
 
     # ------------------------------------------------------------------
@@ -136,6 +144,8 @@ class DecoderModel:
             K.scale_inplace(x32, float(s.embedding_scale))
         if self.position is not None:
             self.position.add_to_stream(x32, ctx)
+        for k, part in enumerate(self.stream_inputs):
+            part.add_to_stream(x32, ctx, caches[len(s.schedule) + k])
         if s.streams is not None:
             # several residual streams, all equal to the embedding at the start; the blocks work on [tokens, streams, width]
             xs = torch.empty((ctx.num_tokens, s.streams, s.hidden_size), dtype=torch.float32, device=self.device)

@@ -29,7 +29,12 @@ Further options of the spec, all off by default:
   mixer then asks for pages and a state slot;
 * ``qk_norm`` (a mapping with the tensor names ``q`` and ``k`` below the prefix, and ``eps``): an RMS norm per head on
   queries and keys, its weight of head size shared by the heads, after the convolution and before the rotation;
-* ``keep_first`` (with a window): the first keys of a sequence stay visible behind the window, at their own positions.
+  With ``whole`` true in the mapping the norm is over the whole projection instead (all heads of q at once, all of k at
+  once, before they are split into heads), with a weight per channel;
+* ``keep_first`` (with a window): the first keys of a sequence stay visible behind the window, at their own positions;
+* ``shared_kv`` true: the layer has no keys and values of its own (no such tensors): it projects queries only and reads
+  the cache that another layer's entry wrote (the schedule entry names it with ``cache_from``), keys as that layer
+  normalised and rotated them.  Head counts and sizes are that layer's.
 """
 
 from __future__ import annotations
@@ -70,36 +75,45 @@ class PagedAttention(Mixer):
         self.taps = int(spec.get("conv") or 0)                # 0: no convolution
         qk_norm = spec.get("qk_norm")
         self.qk_norm_eps = float(qk_norm["eps"]) if qk_norm else 0.0
+        self.norm_whole = bool(qk_norm.get("whole", False)) if qk_norm else False
+        self.shared_kv = bool(spec.get("shared_kv", False))
         if self.num_heads % self.num_kv_heads:
             raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} key/value heads")
         names = spec.get("names", {})
         suffixes = tuple(spec.get("suffixes", (".weight", ".bias")))
         self.q_dim = self.num_heads * self.head_dim
         self.kv_dim = self.num_kv_heads * self.head_dim
-        self.qkv = FusedLinear(
-            prefix, [names.get("q", "q_proj"), names.get("k", "k_proj"), names.get("v", "v_proj")],
-            self.hidden, [self.num_heads * self.qk_dim, self.num_kv_heads * self.qk_dim, self.num_kv_heads * self.value_dim],
-            spec.get("qkv_bias", False), dtype, suffixes=suffixes)
+        stems = [names.get("q", "q_proj"), names.get("k", "k_proj"), names.get("v", "v_proj")]
+        self.real_outs = (self.num_heads * self.qk_dim, self.num_kv_heads * self.qk_dim, self.num_kv_heads * self.value_dim)
+        self.head_shapes = ((self.num_heads, self.qk_dim), (self.num_kv_heads, self.qk_dim), (self.num_kv_heads, self.value_dim))
+        if self.norm_whole and self.taps >= 1:
+            raise ValueError("a norm over the whole projection together with a convolution is not supported")
+        if self.shared_kv:
+            if self.taps >= 1:
+                raise ValueError("a layer that shares another's keys and values cannot have a convolution")
+            stems, self.real_outs, self.head_shapes = stems[:1], self.real_outs[:1], self.head_shapes[:1]
+        self.qkv = FusedLinear(prefix, stems, self.hidden, list(self.real_outs), spec.get("qkv_bias", False), dtype, suffixes=suffixes)
         self.out = FusedLinear(prefix, [names.get("o", "o_proj")], self.num_heads * self.value_dim, [self.hidden],
                                bool(spec.get("out_bias", False)), dtype, suffixes=suffixes)
         gate = spec.get("head_gate")
         self.gate = FusedLinear(prefix, [gate], self.hidden, [self.num_heads], False, dtype, suffixes=suffixes) if gate else None
         position = spec.get("position")
         self.position = POSITIONS.build(position, prefix, dtype, device, head_dim=self.head_dim) if position is not None else None
-        stems = [names.get("q", "q_proj"), names.get("k", "k_proj"), names.get("v", "v_proj")]
         self.conv_names = [prefix + n + str(spec.get("conv_suffix", ".conv")) for n in stems] if self.taps >= 1 else []
-        self.norm_names = [prefix + str(qk_norm[n]) for n in ("q", "k")] if qk_norm else []
+        self.norm_names = [prefix + str(qk_norm[n]) for n in (("q",) if self.shared_kv else ("q", "k"))] if qk_norm else []
         self.conv_weight = self.q_norm = self.k_norm = None
         # what the q|k|v product's epilogues cannot do goes through a kernel of its own behind a plain product
-        self.post = self.taps >= 1 or bool(qk_norm)
+        self.post = self.taps >= 1 or bool(qk_norm) or self.shared_kv
         # steps of single tokens read the convolution's state through the step's device tensors: they can be captured
         self.decodes_from_device = self.taps > 1
-        self.real_outs = (self.num_heads * self.qk_dim, self.num_kv_heads * self.qk_dim, self.num_kv_heads * self.value_dim)
 
     def params(self) -> List[ParamSpec]:
         out = self.qkv.params() + self.out.params() + (self.gate.params() if self.gate is not None else [])
         out += [ParamSpec(n, (o, self.taps), role="vector", mean=1.0 / self.taps, std=0.2) for n, o in zip(self.conv_names, self.real_outs)]
-        out += [ParamSpec(n, (self.qk_dim,), role="vector", init="ones_normal") for n in self.norm_names]
+        if self.norm_whole:
+            out += [ParamSpec(n, (o,), role="vector", init="ones_normal") for n, o in zip(self.norm_names, self.real_outs)]
+        else:
+            out += [ParamSpec(n, (self.qk_dim,), role="vector", init="ones_normal") for n in self.norm_names]
         return out
 
     def parts(self):
@@ -114,13 +128,16 @@ class PagedAttention(Mixer):
         norms = [tensors.pop(n) for n in self.norm_names]
         if self.head_dim != self.qk_dim or self.head_dim != self.value_dim:
             self._pad_heads()
-            shapes = ((self.num_heads, self.qk_dim), (self.num_kv_heads, self.qk_dim), (self.num_kv_heads, self.value_dim))
-            conv = [self._pad_rows(t, *sh) for t, sh in zip(conv, shapes)]
-            norms = [torch.cat([t, torch.zeros(self.head_dim - self.qk_dim, dtype=t.dtype, device=t.device)]) for t in norms]
+            conv = [self._pad_rows(t, *sh) for t, sh in zip(conv, self.head_shapes)]
+            if self.norm_whole:
+                norms = [self._pad_rows(t, *sh) for t, sh in zip(norms, self.head_shapes)]
+            else:
+                norms = [torch.cat([t, torch.zeros(self.head_dim - self.qk_dim, dtype=t.dtype, device=t.device)]) for t in norms]
         if conv:
             self.conv_weight = torch.cat(conv, dim=0).contiguous()
         if norms:
-            self.q_norm, self.k_norm = (t.contiguous() for t in norms)
+            self.q_norm = norms[0].contiguous()
+            self.k_norm = norms[1].contiguous() if len(norms) > 1 else None
 
     def _pad_rows(self, t, heads, d):
         """Rows of a per-channel tensor [heads * d, ...] with zero rows up to the one head size of the cache."""
@@ -139,8 +156,7 @@ class PagedAttention(Mixer):
             out[:, :d] = t.view(heads, d, *t.shape[1:])
             return out.view(heads * D, *t.shape[1:])
 
-        cuts = (nh * self.qk_dim, nkv * self.qk_dim, nkv * self.value_dim)
-        shapes = ((nh, self.qk_dim), (nkv, self.qk_dim), (nkv, self.value_dim))
+        cuts, shapes = tuple(self.real_outs), self.head_shapes
         w = torch.split(self.qkv.weight, cuts, dim=0)
         self.qkv.weight = torch.cat([rows(t, *sh) for t, sh in zip(w, shapes)], dim=0).contiguous()
         if self.qkv.bias is not None:
@@ -154,6 +170,8 @@ class PagedAttention(Mixer):
         self.out.in_features = nh * D
 
     def cache_requirement(self):
+        if self.shared_kv:
+            return None                        # the schedule entry names the entry whose cache this layer reads
         paged = PagedKV(self.num_kv_heads, self.head_dim, self.window, self.keep_first)
         if self.taps > 1:
             # behind the pages: the last taps - 1 rows of the q|k|v projection, which the convolution of the next step reads
@@ -168,7 +186,7 @@ class PagedAttention(Mixer):
         rope = self.position.fused_decode() if self.position is not None else None
         if type(self) is not PagedAttention or rope is None or rope["rotary_dim"] != self.head_dim or self.out.bias is not None:
             return None
-        if self.softcap or self.slopes is not None or self.gate is not None or self.value_dim != self.qk_dim or self.post or self.keep_first:
+        if self.softcap or self.slopes is not None or self.gate is not None or self.value_dim != self.qk_dim or self.post or self.keep_first or self.shared_kv:
             return None
         return {"w_qkv": self.qkv.weight, "b_qkv": self.qkv.bias, "w_o": self.out.weight, "hidden": self.hidden, "heads": self.num_heads,
                 "kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "scale": self.scale, "window": self.window,
@@ -188,7 +206,30 @@ class PagedAttention(Mixer):
         view = ctx.group(cache.group)
         gate = self.gate(h) if self.gate is not None else None        # (a deferred activation: the product applies its factor)
         rot = self.position.rotary(ctx) if self.position is not None else None
-        if self.post:
+        if self.shared_kv and (cache is None or cache.kind != "paged" or cache.writes):
+            raise ValueError(f"attention at {self.prefix!r} shares another layer's keys and values: its schedule entry must name that layer's entry (cache_from)")
+        if self.post and (self.norm_whole or self.shared_kv):
+            # projection; the factors of the norms over the whole of q and of k; then norm, rotation and the cache write as one
+            # kernel.  A layer without keys and values of its own projects queries only, into rows that attention reads as q|k|v.
+            proj = self.qkv(h)
+            T = proj.shape[0]
+            nkv = 0 if self.shared_kv else self.num_kv_heads
+            qkv = proj if not self.shared_kv else torch.empty((T, self.qkv_width), dtype=self.dtype, device=proj.device)
+            rinv = None
+            if self.norm_whole:
+                rinv = torch.empty((T, 2), dtype=torch.float32, device=proj.device)
+                ranges = [(0, self.q_dim, self.num_heads * self.qk_dim)]
+                if not self.shared_kv:
+                    ranges.append((self.q_dim, self.kv_dim, self.num_kv_heads * self.qk_dim))
+                K.row_rinv(proj, ranges, self.qk_norm_eps, rinv)
+            long_step = T >= self.CACHE_WRITE_APART and not self.shared_kv
+            K.conv_norm_rope_kv(proj, qkv, self.conv_weight, None, 0, ctx.q_start, ctx.seq_of_token, ctx.state_slots, self.q_norm, self.k_norm,
+                                self.qk_norm_eps, self.qk_dim, ctx.positions, rot.denominators if rot else None, rot.rotary_dim if rot else 0,
+                                view.slot_mapping, cache.k, cache.v, self.num_heads, nkv, self.head_dim, cache.writes and not self.shared_kv,
+                                to_cache=not long_step, row_rinv=rinv)
+            if long_step and cache.writes:
+                K.rope_kv_write(qkv, ctx.positions, None, 0, view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, True)
+        elif self.post:
             # projection; then convolution, norm per head, rotation and the cache write as one kernel; then the state moves on
             proj = self.qkv(h)
             qkv = torch.empty_like(proj)

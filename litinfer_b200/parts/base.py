@@ -17,6 +17,7 @@ Interfaces:
                  ``gather_forward(x32, rows) -> y[rows]``; ``after_linear(linear, a, x32) -> y``
                  (x32 += linear(a) first; a norm may run it as one kernel with the product)
 * position:      owns what the mixer needs to encode positions (tables, constants)
+* stream input:  ``add_to_stream(x32, ctx, cache)``; ``cache_requirement()``: joins the stream right after the embedding
 * mixer:         ``forward(h, ctx, cache) -> y``; ``cache_requirement()``;
                  optionally ``forward_into(h, ctx, cache, tail) -> h'``
 * feed-forward:  ``forward(h, ctx) -> y``; optionally ``forward_into(h, ctx, tail) -> h'``
@@ -270,6 +271,23 @@ class Position(Part):
         return None
 
 
+class StreamInput(Part):
+    """Something else that joins the residual stream right after the embedding and may keep a state of fixed size per
+    request for it (what it has to remember of a sequence's earlier tokens).  The model owns such parts
+    (``ModelSpec.stream_inputs``); the cache manager gives each what :meth:`cache_requirement` asks for, behind the
+    schedule entries' caches.  Like a mixer with state, it must take a request's tokens in order within a step, and says
+    with ``decodes_from_device`` that it reads the step only through the context's device tensors, so that steps of
+    single tokens can be captured."""
+
+    decodes_from_device = False
+
+    def cache_requirement(self):
+        return None
+
+    def add_to_stream(self, x32: torch.Tensor, ctx, cache) -> None:
+        raise NotImplementedError
+
+
 class Block(Part):
     """``spec`` is a :class:`~litinfer_b200.config.spec.BlockSpec`: parts by role."""
 
@@ -332,4 +350,5 @@ MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITIONS = Registry("position encoding")
+STREAM_INPUTS = Registry("input of the residual stream")
 BLOCKS = Registry("block arrangement")

@@ -6,6 +6,9 @@
     y = sum_e expert_e(w_e h)           ``weight_on`` "input"; or  y = sum_e w_e expert_e(h)  with "output"
     expert(u) = W_down (silu(W_gate u) * (W_up u)), no biases.
 
+``scoring`` "softmax_chosen": the ``top`` largest logits choose a token's experts, and the weights are the softmax over
+the chosen logits alone.  ``router_bias`` true: ``z = W_router h + b``.
+
 How a step runs it: the router's product with a float32 result, the choice per token (one warp a token), a stable
 counting sort of the (token, choice) pairs by expert on the device (in a step of many tokens every expert's run starts
 at a multiple of 128 rows), one gather that builds the experts' input rows in sorted order (with the weight on them), a product per expert over its run of rows for gate|up and for down
@@ -39,8 +42,9 @@ class RoutedExperts(FeedForward):
         self.top = int(spec["top"])
         if not 0 < self.top <= self.experts:
             raise ValueError(f"{self.top} of {self.experts} experts")
-        if spec.get("scoring", "sigmoid") != "sigmoid":
-            raise ValueError(f"routing by '{spec.get('scoring')}' is not supported (sigmoid)")
+        self.scoring = str(spec.get("scoring", "sigmoid"))
+        if self.scoring not in ("sigmoid", "softmax_chosen"):
+            raise ValueError(f"routing by '{spec.get('scoring')}' is not supported (sigmoid, softmax_chosen)")
         self.renormalize = bool(spec.get("renormalize", False))
         if self.renormalize:
             raise ValueError("renormalised routing weights are not supported")
@@ -49,7 +53,8 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"weight_on must be 'input' or 'output', got {self.weight_on!r}")
         n = dict(spec.get("names", {}))
         suffixes = tuple(spec.get("suffixes", (".weight", ".bias")))
-        self.router = FusedLinear(prefix, [n.get("router", "gate")], self.hidden, [self.experts], False, dtype, suffixes=suffixes)
+        self.router = FusedLinear(prefix, [n.get("router", "gate")], self.hidden, [self.experts], bool(spec.get("router_bias", False)), dtype,
+                                  suffixes=suffixes)
         stem = n.get("expert", "experts.{}.")                 # the e-th expert's tensors start with prefix + stem.format(e)
         w = suffixes[0]
         self.expert_names = [tuple(prefix + stem.format(e) + n.get(k, d) + w for k, d in (("gate", "gate_proj"), ("up", "up_proj"), ("down", "down_proj")))
@@ -90,7 +95,7 @@ class RoutedExperts(FeedForward):
         logits = self.router(h, out_dtype=torch.float32)
         ids = torch.empty((T, top), dtype=torch.int32, device=dev)
         weights = torch.empty((T, top), dtype=torch.float32, device=dev)
-        K.moe_route(logits, top, ids, weights)
+        K.moe_route(logits, top, ids, weights, scoring=self.scoring)
         # a step of many tokens: every expert's run of rows starts at a multiple of 128, so that the products run on
         # tensor-core tiles of 128 rows, each of one expert
         pad = self.PAD if (self.dtype == torch.bfloat16 and T * top >= self.PAD_FROM_ROWS) else 1

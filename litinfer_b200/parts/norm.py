@@ -1,6 +1,9 @@
 """RMSNorm: y_j = w_j * x_j / sqrt(mean(x^2) + eps), per token
 (src/ops/rms_norm/op.cpp:13-24).  Sum, reciprocal root and products in
-float32 on the float32 residual stream; one rounding of y to the run dtype."""
+float32 on the float32 residual stream; one rounding of y to the run dtype.
+``gain`` (a parameter of the spec, default 1) is a constant factor on the result, multiplied into the
+weight once when it is bound: a block that adds ``gain * norm(y)`` to the stream.  Kind ``identity``
+is no norm at all: the stream as it is, in the run dtype, for a sublayer that reads the stream itself."""
 
 from __future__ import annotations
 
@@ -32,6 +35,7 @@ class RMSNorm(Norm):
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
         self.tensor = self.prefix + str(spec.get("tensor", "weight"))      # the weight's name below the prefix
+        self.gain = float(spec.get("gain", 1.0))
         self.weight = None
 
     def params(self) -> List[ParamSpec]:
@@ -39,6 +43,8 @@ class RMSNorm(Norm):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors.pop(self.tensor)
+        if self.gain != 1.0:
+            self.weight = (self.weight * self.gain).contiguous()
 
     def fused_decode(self):
         return {"weight": self.weight, "eps": self.eps, "size": self.size} if type(self) is RMSNorm and self.weight is not None else None
@@ -106,6 +112,35 @@ class LayerNorm(Norm):
 
     def statistics(self):
         return (self.weight, True, self.eps)
+
+    def forward(self, x32):
+        out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+        K.norm_add_norm(x32, None, None, self.statistics(), out)
+        return out
+
+    def add_forward(self, x32, delta):
+        out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+        K.norm_add_norm(x32, delta, None, self.statistics(), out)
+        return out
+
+    def gather_forward(self, x32, rows):
+        out = torch.empty((rows.shape[0], x32.shape[1]), dtype=self.dtype, device=x32.device)
+        K.norm_add_norm(x32, None, None, self.statistics(), out, rows=rows)
+        return out
+
+
+@NORMS.register("identity")
+class NoNorm(Norm):
+    """No norm: the residual stream as it is, rounded once to the run dtype.  It stands where an arrangement expects the
+    norm before a sublayer and the design has the sublayer read the stream itself; it has no tensor.  ``statistics()``
+    says so with a weight of None, which :func:`litinfer_b200.kernels.norm_add_norm` takes as "the row as it is"."""
+
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.size = int(spec["size"])
+
+    def statistics(self):
+        return (None, False, 0.0)
 
     def forward(self, x32):
         out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)

@@ -6,6 +6,11 @@ For pair j of the first ``rotary_dim`` elements of a head:
 The part owns the table of denominators ``theta^(2j/rotary_dim)`` (float32);
 the kernel divides the position by it and takes sine and cosine in float32.
 Another frequency rule (scaled, partial) is another table or ``rotary_dim``.
+
+``scaling`` (a mapping with ``factor``, ``low``, ``high``, ``original``) slows the long waves down, by wavelength
+``l = 2 pi * denominator``: below ``original / high`` the frequency stays, beyond ``original / low`` it is divided by
+``factor``, and between the two it is ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``.
+The table of denominators is made once, in float64, and rounded to float32.
 """
 
 from __future__ import annotations
@@ -13,6 +18,26 @@ from __future__ import annotations
 import torch
 
 from .base import POSITIONS, Position, Rotary
+
+
+def scaled_denominators(theta: float, rotary_dim: int, scaling) -> list:
+    """1 / frequency of every pair after the scaling by wavelength (see the module's text), as Python floats."""
+    import math
+
+    factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+    if factor <= 0 or high <= low or original <= 0:
+        raise ValueError(f"rope scaling needs factor > 0, high > low and original > 0, got {dict(scaling)}")
+    out = []
+    for j in range(rotary_dim // 2):
+        f = float(theta) ** (-2.0 * j / rotary_dim)
+        wave = 2.0 * math.pi / f
+        if wave > original / low:
+            f = f / factor
+        elif wave >= original / high:
+            s = (original / wave - low) / (high - low)
+            f = (1.0 - s) * f / factor + s * f
+        out.append(1.0 / f)
+    return out
 
 
 @POSITIONS.register("rope")
@@ -26,8 +51,13 @@ class RotaryEmbedding(Position):
             raise ValueError(f"rope pairing '{pairing}' is not supported (rotate-half only)")
         if self.rotary_dim % 2 or (head_dim is not None and self.rotary_dim > head_dim):
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {head_dim}")
-        j = torch.arange(self.rotary_dim // 2, dtype=torch.float32)
-        denom = torch.pow(torch.tensor(self.theta, dtype=torch.float32), (2.0 * j) / float(self.rotary_dim))
+        scaling = spec.get("scaling")
+        if not scaling:
+            j = torch.arange(self.rotary_dim // 2, dtype=torch.float32)
+            denom = torch.pow(torch.tensor(self.theta, dtype=torch.float32), (2.0 * j) / float(self.rotary_dim))
+        else:
+            denom = torch.tensor(scaled_denominators(self.theta, self.rotary_dim, scaling), dtype=torch.float64).to(torch.float32)
+        self.scaling = dict(scaling) if scaling else None
         self.denominators = denom.to(self.device)
 
     # Steps of more tokens than this get a table of cosines and sines, made once and shared by the layers (products that
@@ -44,7 +74,7 @@ class RotaryEmbedding(Position):
         """``[tokens, rotary_dim / 2, 2]`` float32 cos and sin of this step's positions, or None for a short step."""
         if ctx.num_tokens < self.TABLE_FROM_TOKENS or self.dtype != torch.bfloat16:
             return None
-        key = ("rope_table", self.theta, self.rotary_dim)
+        key = ("rope_table", self.theta, self.rotary_dim, tuple(sorted(self.scaling.items())) if self.scaling else None)
         t = ctx.scratch.get(key)
         if t is None:
             from .. import kernels as K

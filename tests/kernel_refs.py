@@ -230,6 +230,8 @@ def paged_attention_dense(qkv, out, k_cache, v_cache, block_table, q_start, ctx_
 def _norm_of(v, spec):
     weight, centered, eps = spec
     v = v.float()
+    if weight is None:                                    # no norm: the row as it is
+        return v
     if centered:
         v = v - v.mean(-1, keepdim=True)
     return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight
@@ -259,11 +261,12 @@ def rmsnorm_cols(x, col, n, width, weight, eps, out, col_a, col_b=-1):
 
 
 def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions,
-                      denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write=True, shift=False, to_cache=True):
+                      denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write=True, shift=False, to_cache=True,
+                      row_rinv=None):
     if shift and write and conv_w is not None and conv_w.shape[1] > 1:
         # (the state moves on after the convolution has read it: taken care of at the end)
         conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions,
-                          denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write, False, to_cache)
+                          denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write, False, to_cache, row_rinv)
         conv_state_shift(proj, 0, proj.shape[1], conv_w.shape[1], state, state_off, q_start, slots)
         return
     T, N = proj.shape
@@ -287,9 +290,12 @@ def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token
         phi = positions.float()[:, None] / denominators[None, :]
         cos, sin = torch.cos(phi)[:, None, :], torch.sin(phi)[:, None, :]
 
-    def shape(x, weight):
+    def shape(x, weight, which=0):
         x = x.clone()
-        if weight is not None:
+        if weight is not None and row_rinv is not None:
+            # the norm over the whole projection: its factor is given, the weight is per channel
+            x = x * row_rinv[:, which, None, None] * weight.view(1, x.shape[1], x.shape[2])
+        elif weight is not None:
             x = x / torch.sqrt((x * x).sum(-1, keepdim=True) / norm_width + eps) * weight
         if rotary_dim:
             a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
@@ -298,9 +304,9 @@ def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token
         return x
 
     out[:, :q_dim] = shape(u[:, :q_dim].reshape(T, num_heads, head_dim), q_norm).reshape(T, q_dim).to(out.dtype)
-    if not write:
+    if not write or num_kv_heads == 0:
         return
-    k = shape(u[:, q_dim:q_dim + kv_dim].reshape(T, num_kv_heads, head_dim), k_norm).to(out.dtype)
+    k = shape(u[:, q_dim:q_dim + kv_dim].reshape(T, num_kv_heads, head_dim), k_norm, 1).to(out.dtype)
     v = u[:, q_dim + kv_dim:].reshape(T, num_kv_heads, head_dim).to(out.dtype)
     if not to_cache:
         out[:, q_dim:q_dim + kv_dim] = k.reshape(T, kv_dim)
@@ -311,6 +317,29 @@ def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token
     off = (slot_mapping % page_size).long()
     k_cache[page, :, off] = k
     v_cache[page, :, :, off] = v
+
+
+def row_rinv(x, ranges, eps, out):
+    out.zero_()
+    for j, (col, n, width) in enumerate(ranges):
+        v = x[:, col:col + n].float()
+        out[:, j] = 1.0 / torch.sqrt((v * v).sum(-1) / width + eps)
+
+
+def add_pair_rows(x32, pairs, ids, positions, q_start, seq_of_token, slots, state, mul_prev, mul_cur):
+    buckets = pairs.shape[0] - 1
+    starts, sl = q_start.tolist(), slots.tolist()
+    tok, pos = ids.tolist(), positions.tolist()
+    for s in range(len(starts) - 1):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo:
+            continue
+        prev = int(state[sl[s], 0])
+        for t in range(lo, hi):
+            row = buckets if pos[t] == 0 else (prev * int(mul_prev) + tok[t] * int(mul_cur)) % buckets
+            x32[t] += pairs[row].float()
+            prev = tok[t]
+        state[sl[s], 0] = prev
 
 
 def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_cols=0, tile_group=None, epilogue=None):
@@ -331,7 +360,12 @@ def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_c
         out[:, g * out_group_cols:g * out_group_cols + N] = (a[:, g * a_group_cols:g * a_group_cols + Kd].float() @ weight[g].float().t()).to(out.dtype)
 
 
-def moe_route(logits, top, ids, weights):
+def moe_route(logits, top, ids, weights, scoring="sigmoid"):
+    if scoring == "softmax_chosen":
+        order = torch.sort(logits.float(), dim=-1, descending=True, stable=True)
+        ids.copy_(order.indices[:, :top].to(torch.int32))
+        weights.copy_(torch.softmax(order.values[:, :top], dim=-1))
+        return
     s = torch.sigmoid(logits.float())
     E = s.shape[1]
     # the largest scores, the lower index first among equals
@@ -500,13 +534,48 @@ def decay_scan(qkv, q_col, k_col, v_col, decay, state, q_start, slots, out32, he
             out32[t] = torch.einsum("hdv,hd->hv", S, q).reshape(heads * vdim)
 
 
-def gated_rmsnorm(y32, gate, gate_col, weight, eps, groups, gate_first, out):
+def gla_scan(qkv, q_col, k_col, v_col, za, za_col, tau, state, q_start, slots, out32, heads, dim, vdim, chunks=None):
+    starts, sl = q_start.tolist(), slots.tolist()
+    for s in range(len(starts) - 1):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo:
+            continue
+        S = state[sl[s], :heads * dim * vdim].view(heads, vdim, dim).transpose(1, 2)      # kept column by column: [heads][vdim][dim]
+        for t in range(lo, hi):
+            row = qkv[t].float()
+            q = row[q_col:q_col + heads * dim].view(heads, dim) * float(dim) ** -0.5
+            k = row[k_col:k_col + heads * dim].view(heads, dim)
+            v = row[v_col:v_col + heads * vdim].view(heads, vdim)
+            a = torch.exp(torch.nn.functional.logsigmoid(za[t, za_col:za_col + heads * dim].float()) / float(tau)).view(heads, dim)
+            S.mul_(a[:, :, None]).add_(k[:, :, None] * v[:, None, :])
+            out32[t] = torch.einsum("hdv,hd->hv", S, q).reshape(heads * vdim)
+
+
+def channel_scan(x, x_col, bc, b_col, c_col, dt32, z, z_col, A_log, D, state, q_start, slots, y, chunks=None):
+    starts, sl = q_start.tolist(), slots.tolist()
+    inner, N = A_log.shape
+    A = -torch.exp(A_log)
+    for s in range(len(starts) - 1):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo:
+            continue
+        S = state[sl[s], :inner * N].view(inner, N)
+        for t in range(lo, hi):
+            xt = x[t, x_col:x_col + inner].float()
+            B, Cm = bc[t, b_col:b_col + N].float(), bc[t, c_col:c_col + N].float()
+            dt = torch.nn.functional.softplus(dt32[t], threshold=1e9)
+            S.mul_(torch.exp(dt[:, None] * A)).add_((dt * xt)[:, None] * B[None, :])
+            r = S @ Cm + D * xt
+            y[t] = (r * _silu(z[t, z_col:z_col + inner].float())).to(y.dtype)
+
+
+def gated_rmsnorm(y32, gate, gate_col, weight, eps, groups, gate_first, out, gate_act="sigmoid"):
     T, n = y32.shape
     z = gate[:, gate_col:gate_col + n].float()
     v = y32 * _silu(z) if gate_first else y32
     v = v.view(T, groups, n // groups)
     v = (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)).reshape(T, n) * weight
-    _store(out, v if gate_first else v * torch.sigmoid(z))
+    _store(out, v if gate_first else v * (_silu(z) if gate_act == "silu" else torch.sigmoid(z)))
 
 
 def argmax(logits, out):
@@ -598,7 +667,7 @@ def table_gather(resident, updates, slots, out, trash_page):
             out[s, b] = resident[slot, b] if b < cols else trash_page
 
 
-ALL = ["sorted_rows", "norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route", "moe_sort", "moe_gather", "moe_combine",
+ALL = ["row_rinv", "add_pair_rows", "gla_scan", "channel_scan", "sorted_rows", "norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route", "moe_sort", "moe_gather", "moe_combine",
        "glu_clamped", "weighted_sum2", "add_position_rows", "hc_expand", "hc_read_norm", "hc_update", "causal_conv_silu", "conv_state_shift", "ssm_scan",
        "decay_scan", "gated_rmsnorm", "table_gather", "gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]
