@@ -25,8 +25,8 @@ Weights (3 GB) are larger than L2, so nothing stays cached between steps.
 profiling runs and the summaries under ``profiles/``); ``mixed`` is a step of ``--batch`` requests decoding at
 ``--context`` beside a portion of ``--prefill-tokens`` prompt tokens.
 
-``--only design`` runs a design (``--design filasun|gorulorn``, default filasun) beside the Qwen2 model of equal layer sizes and layer count (``--design-shapes``,
-``--layers``, default 6): prefill of ``--prefill-tokens`` tokens and decode at batch 1, 8 and 32; ``--arch filasun|gorulorn`` puts
+``--only design`` runs a design (``--design filasun|gorulorn|demavik``, default filasun) beside the Qwen2 model of equal layer sizes and layer count (``--design-shapes``,
+``--layers``, default 6): prefill of ``--prefill-tokens`` tokens and decode at batch 1, 8 and 32; ``--arch filasun|gorulorn|demavik`` puts
 that design behind ``--only decode|prefill|kernels-decode|kernels-prefill`` (the kernel tables of ``profiles/``).
 
 ``--shape 1.5b|7b|14b`` chooses the layer sizes (default 1.5b, the headline; the other two are the larger workloads of
@@ -128,13 +128,41 @@ def gorulorn_config(shape: str, layers: int, window: int = 1024):
             "max_positions": d["max_position_embeddings"]}
 
 
+def demavik_config(shape: str, layers: int):
+    """A Demavik model with the layer sizes of a shape of the benchmark description: the same width, heads, key/value heads,
+    head size and vocabulary as the Qwen2 model of that shape.  Layers go round four kinds: gated linear attention (keys
+    and values of head size, decays through a rank of 16), grouped-query attention (norms over the whole projections,
+    whole heads rotated with scaled frequencies), the same reading the keys and values of the layer before it, and a
+    selective scan with a state row per channel (twice the width, a state of 16, 4 taps); every layer has 8 experts of
+    half the dense feed-forward width, 2 per token; an embedding of token pairs with 32,749 buckets."""
+    d = SHAPES[shape]
+    H, nh, nkv, dh = d["hidden_size"], d["num_attention_heads"], d["num_key_value_heads"], d["head_dim"]
+    mlp = {"kind": "moe", "expert": {"ff": d["intermediate_size"] // 2}, "router": {"experts": 8, "top": 2}}
+    rot = {"dims": dh, "base": d["rope_theta"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    att = {"heads": nh, "kv_heads": nkv, "dim": dh, "vdim": dh, "rot": rot, "scale": dh ** -0.5}
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        if kind == 0:
+            out.append({"type": "gla", "mlp": mlp, "mixer": {"heads": nh, "dim": dh, "vdim": dh, "tau": 16.0, "decay_rank": 16}})
+        elif kind == 1:
+            out.append({"type": "attention", "mlp": mlp, "mixer": dict(att)})
+        elif kind == 2:
+            out.append({"type": "attention", "mlp": mlp, "mixer": dict(att, kv_from=i - 1)})
+        else:
+            out.append({"type": "mamba1", "mlp": mlp, "mixer": {"inner": 2 * H, "state": 16, "dt_rank": H // 16, "conv": 4}})
+    return {"architecture": "Demavik", "embedding": {"scale": 2.0, "bigram": {"buckets": 32749, "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": out, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "vocab": d["vocab_size"], "width": H,
+            "max_positions": d["max_position_embeddings"]}
+
+
 def design_layer_runs(cfg) -> int:
     loop = cfg.get("loop")
     return len(cfg["layers"]) + ((loop["stop"] - loop["start"]) * (loop["times"] - 1) if loop else 0)
 
 
 def time_design(args, peaks):
-    """Prefill and decode of a design (``--design filasun|gorulorn``) beside the Qwen2 model of the same layer sizes and as
+    """Prefill and decode of a design (``--design filasun|gorulorn|demavik``) beside the Qwen2 model of the same layer sizes and as
     many layers as the design runs (random weights), through the same step function: tokens per second, and the
     milliseconds behind them."""
     import torch
@@ -153,6 +181,8 @@ def time_design(args, peaks):
             elif arch == "gorulorn":
                 cfg = gorulorn_config(shape, layers)
                 runs = design_layer_runs(cfg)
+            elif arch == "demavik":
+                cfg = demavik_config(shape, layers)
             else:
                 cfg = bench_config(shape)
                 cfg["num_hidden_layers"] = runs
@@ -749,8 +779,8 @@ def main() -> int:
                          "a portion of --prefill-tokens prompt tokens")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (so that a profiler lists them)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--design", default="filasun", choices=["filasun", "gorulorn"], help="--only design: the design that runs beside Qwen2")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "filasun", "gorulorn"],
+    ap.add_argument("--design", default="filasun", choices=["filasun", "gorulorn", "demavik"], help="--only design: the design that runs beside Qwen2")
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "filasun", "gorulorn", "demavik"],
                     help="which design the parts behind --only are measured on, with the layer sizes of --shape (default: the headline's Qwen2)")
     ap.add_argument("--design-shapes", default="1.5b,7b", help="--only design: the shapes whose layer sizes are run, with commas")
     args = ap.parse_args()
@@ -792,6 +822,13 @@ def main() -> int:
             return 2
         cfg = gorulorn_config(args.shape, args.layers or 6)
         cfg["num_hidden_layers"], cfg["max_position_embeddings"] = design_layer_runs(cfg), cfg["max_positions"]
+        cfg.update(num_key_value_heads=0, head_dim=0, hidden_size=cfg["width"])
+    if args.arch == "demavik":
+        if args.only == "all":
+            print("bench.py: --arch demavik goes with --only decode|prefill|kernels-decode|kernels-prefill|design")
+            return 2
+        cfg = demavik_config(args.shape, args.layers or 6)
+        cfg["num_hidden_layers"], cfg["max_position_embeddings"] = len(cfg["layers"]), cfg["max_positions"]
         cfg.update(num_key_value_heads=0, head_dim=0, hidden_size=cfg["width"])
     if args.only in ("decode", "kernels-decode") and args.context + 4096 > cfg["max_position_embeddings"]:
         # a longer context than the shape's own limit, on request: the measurement's model allows it
