@@ -552,6 +552,110 @@ channel_scan_kernel(const T* __restrict__ x, int x_stride, int x_off, const T* _
     }
 }
 
+// The same scan for states of up to 64 elements, a channel per thread: the channel's whole state row and its rates stay in
+// the thread's registers (NB of each, N <= NB, the rest zeros that stay zeros), so the sum over the state is a chain of
+// multiply-adds inside the thread and nothing crosses lanes.  With a state of 16 the form above leaves half of every warp
+// idle and pays nine shuffles a token for eight short sums.  B and C of kStage tokens are staged once a block (every thread
+// reads the same address: one 16-byte load serves the warp); step sizes, inputs and gates are staged by the thread that
+// uses them, with softplus and silu applied.  Same arguments, passes and state layout as channel_scan_kernel.
+constexpr int kLaneChannels = 128;      // threads of a block, a channel each
+
+template <typename T, int NB>
+__global__ void __launch_bounds__(kLaneChannels)
+channel_scan_lane_kernel(const T* __restrict__ x, int x_stride, int x_off, const T* __restrict__ bc, int bc_stride, int b_off, int c_off,
+                         const float* __restrict__ dt_raw, int dt_stride, const T* __restrict__ z, int z_stride, int z_off,
+                         const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ state, long long state_stride,
+                         const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ y, int inner, int N,
+                         const int* __restrict__ seg, int mode, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
+    __shared__ __align__(16) float Bs[kStage][NB];
+    __shared__ __align__(16) float Cs[kStage][NB];
+    __shared__ float xs[kStage][kLaneChannels];
+    __shared__ float dts[kStage][kLaneChannels];
+    __shared__ float gs[kStage][kLaneChannels];         // silu of the gate
+    pdl_launch_dependents();
+    pdl_wait();
+    const Piece pc = piece_of(seg, q_start, slots);
+    const int q0 = pc.q0, q1 = pc.q1;
+    if (q1 <= q0) return;
+    const int tid = threadIdx.x;
+    const int c = blockIdx.x * kLaneChannels + tid;
+    const bool live = c < inner;
+    float* st = state + (size_t)pc.slot * state_stride;
+    float* cst = chunk_state ? chunk_state + (size_t)pc.chunk * inner * N : nullptr;
+    const float* from = mode == kScanWhole ? st : cst;
+    float S[NB], rate[NB];
+#pragma unroll
+    for (int n = 0; n < NB; ++n) {
+        const bool in = live && n < N;
+        const size_t at = (size_t)c * N + n;
+        S[n] = (mode != kScanLocal && in) ? from[at] : 0.0f;
+        rate[n] = in ? -expf(A_log[at]) * 1.4426950408889634f : 0.0f;
+    }
+    const float dc = live ? D[c] : 0.0f;
+    float dtsum = 0.0f;
+    for (int t0 = q0; t0 < q1; t0 += kStage) {
+        const int nt = min(kStage, q1 - t0);
+        __syncthreads();                                   // the stage before has been used up
+        for (int e = tid; e < nt * NB; e += kLaneChannels) {
+            const int tk = e / NB, n = e - tk * NB;
+            const T* row = bc + (size_t)(t0 + tk) * bc_stride;
+            Bs[tk][n] = n < N ? to_float(row[b_off + n]) : 0.0f;
+            if (mode != kScanLocal) Cs[tk][n] = n < N ? to_float(row[c_off + n]) : 0.0f;
+        }
+        if (live) {
+#pragma unroll 4
+            for (int tk = 0; tk < nt; ++tk) {
+                xs[tk][tid] = to_float(x[(size_t)(t0 + tk) * x_stride + x_off + c]);
+                dts[tk][tid] = softplus_f(dt_raw[(size_t)(t0 + tk) * dt_stride + c]);
+                if (mode != kScanLocal) gs[tk][tid] = silu_f(to_float(z[(size_t)(t0 + tk) * z_stride + z_off + c]));
+            }
+        }
+        __syncthreads();
+        if (!live) continue;
+        for (int tk = 0; tk < nt; ++tk) {
+            const float dt = dts[tk][tid], xv = xs[tk][tid], dx = dt * xv;
+            if (mode == kScanLocal) {
+                dtsum += dt;
+#pragma unroll
+                for (int n = 0; n < NB; n += 4) {
+                    const float4 b = *reinterpret_cast<const float4*>(&Bs[tk][n]);
+                    S[n] = fmaf(exp2f(dt * rate[n]), S[n], b.x * dx);
+                    S[n + 1] = fmaf(exp2f(dt * rate[n + 1]), S[n + 1], b.y * dx);
+                    S[n + 2] = fmaf(exp2f(dt * rate[n + 2]), S[n + 2], b.z * dx);
+                    S[n + 3] = fmaf(exp2f(dt * rate[n + 3]), S[n + 3], b.w * dx);
+                }
+                continue;
+            }
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;       // four sums side by side, always added in the same order
+#pragma unroll
+            for (int n = 0; n < NB; n += 4) {
+                const float4 b = *reinterpret_cast<const float4*>(&Bs[tk][n]);
+                const float4 cc = *reinterpret_cast<const float4*>(&Cs[tk][n]);
+                S[n] = fmaf(exp2f(dt * rate[n]), S[n], b.x * dx);
+                S[n + 1] = fmaf(exp2f(dt * rate[n + 1]), S[n + 1], b.y * dx);
+                S[n + 2] = fmaf(exp2f(dt * rate[n + 2]), S[n + 2], b.z * dx);
+                S[n + 3] = fmaf(exp2f(dt * rate[n + 3]), S[n + 3], b.w * dx);
+                a0 = fmaf(S[n], cc.x, a0);
+                a1 = fmaf(S[n + 1], cc.y, a1);
+                a2 = fmaf(S[n + 2], cc.z, a2);
+                a3 = fmaf(S[n + 3], cc.w, a3);
+            }
+            const float r = fmaf(dc, xv, (a0 + a1) + (a2 + a3));
+            y[(size_t)(t0 + tk) * inner + c] = from_float<T>(r * gs[tk][tid]);
+        }
+    }
+    if (mode != kScanApply && live) {
+        float* to = mode == kScanWhole ? st : cst;
+#pragma unroll
+        for (int n = 0; n < NB; ++n)
+            if (n < N) {
+                const size_t at = (size_t)c * N + n;
+                to[at] = S[n];
+                if (mode == kScanLocal) chunk_decay[(size_t)pc.chunk * inner * N + at] = exp2f(dtsum * rate[n]);
+            }
+    }
+}
+
 // Between the two passes over chunks: for each run of chunks (a sequence's, in order) S starts as the slot's state;
 // chunk_state[chunk] (the chunk's end state from zeros) is replaced by the state the chunk starts from, and
 // S <- decay[chunk, head] S + end state.  The last S goes back to the slot.
@@ -619,6 +723,49 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const T* __res
         else if (mode == 1) v = (v * rinv * w[g * gs + j]) * sigmoid_f(z);
         else v = (v * rinv * w[g * gs + j]) * silu_f(z);
         o[j] = from_float<T>(v);
+    }
+}
+
+// The same for groups of up to kWarpGroup elements (a head's output): a warp per (token, group), eight of them a block, no
+// barrier; a lane keeps its elements (with the gate applied where it comes first) between the sum and the result.
+constexpr int kWarpGroup = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_warp_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride, int gate_off, const float* __restrict__ w,
+                          float eps, int mode, T* __restrict__ out, int n, int groups, long long rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const long long t = r / groups;
+    const int g = (int)(r - t * groups);
+    const int gs = n / groups;
+    const float* yr = y + (size_t)t * n + (size_t)g * gs;
+    const T* zr = gate + (size_t)t * gate_stride + gate_off + (size_t)g * gs;
+    constexpr int kPer = kWarpGroup / 32;
+    float v[kPer], zz[kPer];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const int j = lane + 32 * i;
+        v[i] = j < gs ? yr[j] : 0.0f;
+        zz[i] = j < gs ? to_float(zr[j]) : 0.0f;
+        if (mode == 0) v[i] *= silu_f(zz[i]);
+        ss += v[i] * v[i];
+    }
+    ss = warp_sum(ss);
+    const float rinv = 1.0f / sqrtf(ss / (float)gs + eps);
+    T* o = out + (size_t)t * n + (size_t)g * gs;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const int j = lane + 32 * i;
+        if (j >= gs) break;
+        float u = v[i] * rinv * w[g * gs + j];
+        if (mode == 1) u *= sigmoid_f(zz[i]);
+        else if (mode == 2) u *= silu_f(zz[i]);
+        o[j] = from_float<T>(u);
     }
 }
 
@@ -796,6 +943,18 @@ static int launch_channel(const void* x, int x_stride, int x_off, const void* bc
     return li_check_launch("channel_scan");
 }
 
+template <typename T, int NB>
+static int launch_channel_lane(const void* x, int x_stride, int x_off, const void* bc, int bc_stride, int b_off, int c_off, const float* dt_raw,
+                               int dt_stride, const void* z, int z_stride, int z_off, const float* A_log, const float* D, float* state,
+                               long long state_stride, const int* q_start, const int* slots, void* y, int S, int inner, int N, const int* seg,
+                               int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
+    cudaError_t e = li_launch_pdl(channel_scan_lane_kernel<T, NB>, dim3(ceil_div(inner, kLaneChannels), 1, S), dim3(kLaneChannels), 0, stream,
+                                  (const T*)x, x_stride, x_off, (const T*)bc, bc_stride, b_off, c_off, dt_raw, dt_stride, (const T*)z, z_stride, z_off,
+                                  A_log, D, state, state_stride, q_start, slots, (T*)y, inner, N, seg, mode, chunk_state, chunk_decay);
+    if (e != cudaSuccess) return li_fail("channel_scan: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("channel_scan");
+}
+
 // The state of a slot: [inner][N].  chunk_decay: [chunks, inner, N].
 LI_EXPORT int li_channel_scan(const void* x, int dtype, int x_stride, int x_off, const void* bc, int bc_stride, int b_off, int c_off,
                               const float* dt_raw, int dt_stride, const void* z, int z_stride, int z_off, const float* A_log, const float* D,
@@ -816,10 +975,22 @@ LI_EXPORT int li_channel_scan(const void* x, int dtype, int x_stride, int x_off,
                            : launch_channel<bf16, RR>(x, x_stride, x_off, bc, bc_stride, b_off, c_off, dt_raw, dt_stride, z, z_stride, z_off, A_log,  \
                                                       D, state, state_stride, q_start, slots, y, S, inner, N, seg, mode, chunk_state, chunk_decay,  \
                                                       stream)
-    if (N <= 32) { LI_SCAN(1); }
-    if (N <= 64) { LI_SCAN(2); }
+#define LI_LANE(NB)                                                                                                                              \
+    return dtype == LI_F32 ? launch_channel_lane<float, NB>(x, x_stride, x_off, bc, bc_stride, b_off, c_off, dt_raw, dt_stride, z, z_stride, z_off, \
+                                                            A_log, D, state, state_stride, q_start, slots, y, S, inner, N, seg, mode, chunk_state, \
+                                                            chunk_decay, stream)                                                                 \
+                           : launch_channel_lane<bf16, NB>(x, x_stride, x_off, bc, bc_stride, b_off, c_off, dt_raw, dt_stride, z, z_stride, z_off,  \
+                                                           A_log, D, state, state_stride, q_start, slots, y, S, inner, N, seg, mode, chunk_state,  \
+                                                           chunk_decay, stream)
+    // up to 64 state elements: a channel per thread, its row in registers; beyond: a warp per eight channels
+    if (N <= 4) { LI_LANE(4); }
+    if (N <= 8) { LI_LANE(8); }
+    if (N <= 16) { LI_LANE(16); }
+    if (N <= 32) { LI_LANE(32); }
+    if (N <= 64) { LI_LANE(64); }
     if (N <= 128) { LI_SCAN(4); }
     LI_SCAN(8);
+#undef LI_LANE
 #undef LI_SCAN
 }
 
@@ -848,6 +1019,17 @@ LI_EXPORT int li_gated_rmsnorm(const float* y, const void* gate, int dtype, int 
     const long long blocks = (long long)T * groups;
     LI_REQUIRE(blocks < (1LL << 31), "gated norm: too many rows");
     cudaError_t e;
+    if (n / groups <= kWarpGroup && (dtype == LI_F32 || dtype == LI_BF16)) {
+        const dim3 grid((unsigned)((blocks + 7) / 8));
+        if (dtype == LI_F32)
+            e = li_launch_pdl(gated_rmsnorm_warp_kernel<float>, grid, dim3(256), 0, stream, y, (const float*)gate, gate_stride, gate_off, w, eps, mode,
+                              (float*)out, n, groups, blocks);
+        else
+            e = li_launch_pdl(gated_rmsnorm_warp_kernel<bf16>, grid, dim3(256), 0, stream, y, (const bf16*)gate, gate_stride, gate_off, w, eps, mode,
+                              (bf16*)out, n, groups, blocks);
+        if (e != cudaSuccess) return li_fail("gated_rmsnorm: launch failed: %s", cudaGetErrorString(e));
+        return li_check_launch("gated_rmsnorm");
+    }
     if (dtype == LI_F32)
         e = li_launch_pdl(gated_rmsnorm_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, y, (const float*)gate, gate_stride, gate_off, w, eps,
                           mode, (float*)out, n, groups);
