@@ -378,14 +378,10 @@ gla_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int
 #pragma unroll
         for (int e = 0; e < E; ++e)
             S[j][e] = (mode != kScanLocal && col0 + j < dv && E * lane + e < d) ? from[(size_t)(col0 + j) * d + E * lane + e] : 0.0f;
-    if (mode == kScanLocal && blockIdx.x == 0) {
-        // the chunk's decay per key channel, for the pass that carries states from chunk to chunk: the logarithms are summed
-        for (int i = threadIdx.x; i < d; i += blockDim.x) {
-            float sum = 0.0f;
-            for (int t = q0; t < q1; ++t) sum += -softplus_f(-za[(size_t)t * za_stride + za_off + h * d + i]) * inv_tau;
-            chunk_decay[((size_t)pc.chunk * heads + h) * d + i] = expf(sum);
-        }
-    }
+    // the chunk's decay per key channel, for the pass that carries states from chunk to chunk: the logarithms of its tokens'
+    // decays, summed in the order of the tokens from the staged rows (the pass from zeros stages them where q would stand)
+    float logsum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    const bool sums = mode == kScanLocal && blockIdx.x == 0;
     for (int t0 = q0; t0 < q1; t0 += kStage) {
         const int nt = min(kStage, q1 - t0);
         __syncthreads();
@@ -393,9 +389,10 @@ gla_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int
             const T* row = qkv + (size_t)(t0 + tk) * stride;
             const float* zrow = za + (size_t)(t0 + tk) * za_stride + za_off + h * d;
             for (int i = lane; i < DP; i += 32) {
-                if (mode != kScanLocal) qs[tk * DP + i] = i < d ? to_float(row[q_off + h * d + i]) * q_scale : 0.0f;
+                const float lg = i < d ? -softplus_f(-zrow[i]) * inv_tau : 0.0f;
+                qs[tk * DP + i] = mode == kScanLocal ? lg : i < d ? to_float(row[q_off + h * d + i]) * q_scale : 0.0f;
                 ks[tk * DP + i] = i < d ? to_float(row[k_off + h * d + i]) : 0.0f;
-                as[tk * DP + i] = i < d ? expf(-softplus_f(-zrow[i]) * inv_tau) : 0.0f;
+                as[tk * DP + i] = i < d ? expf(lg) : 0.0f;
             }
         }
         for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
@@ -404,6 +401,14 @@ gla_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int
             vs[e] = c < dv ? to_float(qkv[(size_t)(t0 + tk) * stride + v_off + h * dv + c]) : 0.0f;
         }
         __syncthreads();
+        if (sums) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = threadIdx.x + u * blockDim.x;
+                if (i < d)
+                    for (int tk = 0; tk < nt; ++tk) logsum[u] += qs[tk * DP + i];
+            }
+        }
 #pragma unroll 2
         for (int tk = 0; tk < nt; ++tk) {
             float kk[E], aa[E], v[kWarpCols];
@@ -431,6 +436,13 @@ gla_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int
             const float total = sum8_across_warp(acc, lane);
             const int j = column_after_sum8(lane);
             if ((lane & 3) == 0 && col0 + j < dv) out[(size_t)(t0 + tk) * heads * dv + h * dv + col0 + j] = total;
+        }
+    }
+    if (sums) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = threadIdx.x + u * blockDim.x;
+            if (i < d) chunk_decay[((size_t)pc.chunk * heads + h) * d + i] = expf(logsum[u]);
         }
     }
     if (mode != kScanApply) {

@@ -58,7 +58,7 @@ def config(layers, width=48, vocab=97, eps=1e-5, mult=0.7, scale=2.5, bigram=(13
 
 
 # ranks of the decays' maps: config.json does not give them, the stored shape does (layer index -> rank)
-RANKS = {"mixed": {2: 5}, "gla_only": {0: 7}, "ones": {1: 1}, "far": {0: 4}, "shared_first": {1: 3}}
+RANKS = {"mixed": {2: 5}, "gla_only": {0: 7}, "ones": {1: 1}, "far": {0: 4}, "shared_first": {1: 3}, "odd": {1: 3}, "wide": {0: 8}}
 
 CONFIGS = {
     # everything at once, no two sizes alike: value heads wider and narrower than key heads, three query heads per key
@@ -88,6 +88,17 @@ CONFIGS = {
     "ones": config([attention(heads=1, kv=1, dim=16, vdim=16, rot=2, scaling=None, scale=1.0, mlp=moe(1, 1, 8)),
                     gla(heads=1, dim=8, vdim=8, tau=1.0, mlp=None), mamba(inner=8, state=1, dt_rank=1, conv=1, mlp=None)],
                    width=16, vocab=17, mult=1.0, scale=1.0, bigram=(1, 2, 3)),
+    # sizes that are multiples of nothing much: a width of 36, heads of 12, 20, 10 and 6, 18 channels with a state of 5
+    "odd": config([attention(heads=3, kv=1, dim=12, vdim=20, rot=6, scale=0.4, mlp=moe(3, 2, 12)), gla(heads=2, dim=10, vdim=6, tau=3.0, mlp=None),
+                   mamba(inner=18, state=5, dt_rank=3, conv=2, mlp=moe(3, 2, 12)), attention(heads=3, kv=1, dim=12, vdim=20, rot=6, scale=0.4, kv_from=0, mlp=None)],
+                  width=36, vocab=35, bigram=(11, 5, 3)),
+    # sizes of a model's layers, where the tensor-core kernels take the heads (64 and 128) and the experts' products
+    "wide": config([gla(heads=2, dim=64, vdim=128, tau=8.0, mlp=moe(8, 2, 64)),
+                    attention(heads=4, kv=2, dim=64, vdim=64, rot=64, base=10000.0, scaling=(4.0, 1.0, 4.0, 256), scale=0.125, mlp=moe(8, 2, 64)),
+                    attention(heads=4, kv=2, dim=64, vdim=64, rot=64, base=10000.0, scaling=(4.0, 1.0, 4.0, 256), scale=0.125, kv_from=1, mlp=None),
+                    mamba(inner=512, state=16, dt_rank=16, conv=4, mlp=moe(8, 2, 64)),
+                    attention(heads=2, kv=1, dim=128, vdim=128, rot=32, base=50000.0, scaling=None, scale=0.09, mlp=None)],
+                   width=256, vocab=512, mult=0.5, scale=3.0, bigram=(509, 127, 17)),
     # states that forget slowly (see make_weights) and full attention: a token far back still moves the last logits
     "far": config([gla(heads=2, dim=16, vdim=16, tau=16.0, mlp=None), attention(heads=2, kv=1, dim=16, vdim=16, rot=16, mlp=None)],
                   width=32, vocab=41),
@@ -289,6 +300,36 @@ def test_whole_decoded_and_in_portions(dtype, device, folders, request):
         assert (run.logits("whole") - run.logits("tail")).abs().max() < 1e-4
     run.rp.manager.check()
     assert run.rp.manager.num_free_slots() == 4
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["odd", "wide"])
+def test_other_sizes_whole_decoded_and_in_portions(name, dtype, device, folders, request):
+    """Sizes that are multiples of nothing, and sizes of a real model's layers (on a GPU: the kernels for heads of 64 and
+    128, for long portions and for many experts' rows): a prompt whole, its end decoded, and in portions."""
+    dev = use_device(device, request)
+    folder, cfg, w = folders[name]
+    n = 330 if device == "cuda" else 70
+    toks = random_tokens(n, cfg["vocab"], 23)
+    ref = oracle(name, cfg, w, toks, dtype)
+    run = Run(folder, dtype, dev, 384)
+    run.step([("whole", toks, n)], end=["whole"])
+    assert_close(run.logits("whole"), ref, dtype, f"{name} whole")
+    run.step([("tail", toks, n - 40)])
+    for i in range(40):
+        run.step([("tail", toks, 1)], end=["tail"] if i == 39 else [])
+    assert_close(run.logits("tail"), ref, dtype, f"{name} decoded")
+    fed, i, sizes = 0, 0, [3, 64, 2, 129, 17, 1, 70]
+    while fed < n:
+        c = min(sizes[i % len(sizes)], n - fed)
+        run.step([("cut", toks, c)], end=["cut"] if fed + c == n else [])
+        fed += c
+        i += 1
+    assert_close(run.logits("cut"), ref, dtype, f"{name} portions")
+    if dtype == "float32":
+        assert (run.logits("whole") - run.logits("cut")).abs().max() < 2e-4
+    run.rp.manager.check()
 
 
 @pytest.mark.parametrize("device", DEVICES)
@@ -537,7 +578,10 @@ def test_gated_linear_attention_scan_kernel(heads, d, dv, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("inner,N,rank", [(40, 12, 3), (8, 1, 1), (70, 33, 5), (256, 16, 8), (24, 130, 2)])
+# states of up to 64 elements run with a channel per thread (rows of 4, 8, 16, 32 and 64 registers), larger ones with a
+# warp per eight channels: sizes that fill a row exactly, that leave part of it empty, and blocks of channels with a ragged end
+@pytest.mark.parametrize("inner,N,rank", [(40, 12, 3), (8, 1, 1), (70, 33, 5), (256, 16, 8), (24, 130, 2), (200, 32, 2), (130, 64, 4), (33, 5, 1),
+                                          (16, 65, 1)])
 def test_selective_scan_with_a_state_row_per_channel_kernel(inner, N, rank, dtype):
     import kernel_refs as R
     from litinfer_b200 import kernels as K
@@ -567,6 +611,28 @@ def test_selective_scan_with_a_state_row_per_channel_kernel(inner, N, rank, dtyp
             _close(st, outs[2][0], dtype, f"states ({how})", 1e-4)
             assert torch.equal(st[4], state[4]) and torch.equal(st[:, inner * N:], state[:, inner * N:])
         state = outs[2][0]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,groups,size", [(37, 3, 24), (9, 12, 128), (5, 2, 512), (5, 2, 513), (3, 1, 1200), (70, 1, 1)])
+def test_gated_norm_kernel_in_short_and_long_groups(T, groups, size, dtype):
+    """Groups of up to 512 elements are normed by a warp each, longer ones by a block: both against the plain reference,
+    with the gate before the norm and (as a sigmoid or a silu) after it."""
+    import kernel_refs as R
+    from litinfer_b200 import kernels as K
+
+    dev, dt = torch.device("cuda:0"), _dt(dtype)
+    torch.manual_seed(T + size)
+    n = groups * size
+    y32 = torch.randn(T, n, device=dev) * 3.0
+    gate = torch.randn(T, n + 11, device=dev).to(dt)
+    w = (1.0 + 0.3 * torch.randn(n, device=dev))
+    for first, act in ((True, "sigmoid"), (False, "sigmoid"), (False, "silu")):
+        a, b = (torch.empty(T, n, device=dev, dtype=dt) for _ in range(2))
+        K.gated_rmsnorm(y32, gate, 5, w, 1e-5, groups, first, a, gate_act=act)
+        R.gated_rmsnorm(y32, gate, 5, w, 1e-5, groups, first, b, gate_act=act)
+        _close(a, b, dtype, f"gated norm, gate first {first}, {act}")
 
 
 @pytest.mark.gpu
