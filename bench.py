@@ -777,6 +777,7 @@ def main() -> int:
                     help="measure one part and print a short line (for profiling runs); kernels-*: a table of the "
                          "kernels' device times from torch.profiler; mixed: --batch requests decoding at --context beside "
                          "a portion of --prefill-tokens prompt tokens")
+    ap.add_argument("--kernel-rows", type=int, default=16, help="--only kernels-*: how many kernels the table lists")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (so that a profiler lists them)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--design", default="filasun", choices=["filasun", "gorulorn", "demavik"], help="--only design: the design that runs beside Qwen2")
@@ -863,7 +864,7 @@ def main() -> int:
             with profile(activities=[ProfilerActivity.CUDA]) as prof:
                 ms = time_prefill(model, args.prefill_tokens, repeats=1, graphs=False)
             print(json.dumps({"only": args.only, "tokens": args.prefill_tokens, "ms": round(ms, 3), "runs_in_table": 3}))
-        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=16, max_name_column_width=70))
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=args.kernel_rows, max_name_column_width=70))
         return 0
     if args.only == "decode":
         r = time_decode(model, args.batch, args.context, args.steps, warmup, graphs=not args.no_graphs)

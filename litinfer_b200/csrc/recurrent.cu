@@ -569,7 +569,8 @@ channel_scan_kernel(const T* __restrict__ x, int x_stride, int x_off, const T* _
 // multiply-adds inside the thread and nothing crosses lanes.  With a state of 16 the form above leaves half of every warp
 // idle and pays nine shuffles a token for eight short sums.  B and C of kStage tokens are staged once a block (every thread
 // reads the same address: one 16-byte load serves the warp); step sizes, inputs and gates are staged by the thread that
-// uses them, with softplus and silu applied.  Same arguments, passes and state layout as channel_scan_kernel.
+// uses them, with softplus and silu applied.  A token's decays are ex2.approx of a product that is never positive (a result
+// below the smallest normal float is zero).  Same arguments, passes and state layout as channel_scan_kernel.
 constexpr int kLaneChannels = 128;      // threads of a block, a channel each
 
 template <typename T, int NB>
@@ -615,7 +616,7 @@ channel_scan_lane_kernel(const T* __restrict__ x, int x_stride, int x_off, const
             if (mode != kScanLocal) Cs[tk][n] = n < N ? to_float(row[c_off + n]) : 0.0f;
         }
         if (live) {
-#pragma unroll 4
+#pragma unroll 8
             for (int tk = 0; tk < nt; ++tk) {
                 xs[tk][tid] = to_float(x[(size_t)(t0 + tk) * x_stride + x_off + c]);
                 dts[tk][tid] = softplus_f(dt_raw[(size_t)(t0 + tk) * dt_stride + c]);
@@ -631,10 +632,10 @@ channel_scan_lane_kernel(const T* __restrict__ x, int x_stride, int x_off, const
 #pragma unroll
                 for (int n = 0; n < NB; n += 4) {
                     const float4 b = *reinterpret_cast<const float4*>(&Bs[tk][n]);
-                    S[n] = fmaf(exp2f(dt * rate[n]), S[n], b.x * dx);
-                    S[n + 1] = fmaf(exp2f(dt * rate[n + 1]), S[n + 1], b.y * dx);
-                    S[n + 2] = fmaf(exp2f(dt * rate[n + 2]), S[n + 2], b.z * dx);
-                    S[n + 3] = fmaf(exp2f(dt * rate[n + 3]), S[n + 3], b.w * dx);
+                    S[n] = fmaf(fast_exp2(dt * rate[n]), S[n], b.x * dx);
+                    S[n + 1] = fmaf(fast_exp2(dt * rate[n + 1]), S[n + 1], b.y * dx);
+                    S[n + 2] = fmaf(fast_exp2(dt * rate[n + 2]), S[n + 2], b.z * dx);
+                    S[n + 3] = fmaf(fast_exp2(dt * rate[n + 3]), S[n + 3], b.w * dx);
                 }
                 continue;
             }
@@ -643,10 +644,10 @@ channel_scan_lane_kernel(const T* __restrict__ x, int x_stride, int x_off, const
             for (int n = 0; n < NB; n += 4) {
                 const float4 b = *reinterpret_cast<const float4*>(&Bs[tk][n]);
                 const float4 cc = *reinterpret_cast<const float4*>(&Cs[tk][n]);
-                S[n] = fmaf(exp2f(dt * rate[n]), S[n], b.x * dx);
-                S[n + 1] = fmaf(exp2f(dt * rate[n + 1]), S[n + 1], b.y * dx);
-                S[n + 2] = fmaf(exp2f(dt * rate[n + 2]), S[n + 2], b.z * dx);
-                S[n + 3] = fmaf(exp2f(dt * rate[n + 3]), S[n + 3], b.w * dx);
+                S[n] = fmaf(fast_exp2(dt * rate[n]), S[n], b.x * dx);
+                S[n + 1] = fmaf(fast_exp2(dt * rate[n + 1]), S[n + 1], b.y * dx);
+                S[n + 2] = fmaf(fast_exp2(dt * rate[n + 2]), S[n + 2], b.z * dx);
+                S[n + 3] = fmaf(fast_exp2(dt * rate[n + 3]), S[n + 3], b.w * dx);
                 a0 = fmaf(S[n], cc.x, a0);
                 a1 = fmaf(S[n + 1], cc.y, a1);
                 a2 = fmaf(S[n + 2], cc.z, a2);
