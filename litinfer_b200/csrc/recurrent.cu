@@ -743,7 +743,7 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const T* __res
 // barrier; a lane keeps its elements (with the gate applied where it comes first) between the sum and the result.
 constexpr int kWarpGroup = 512;
 
-template <typename T>
+template <typename T, bool kVec4>
 __global__ void __launch_bounds__(256)
 gated_rmsnorm_warp_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride, int gate_off, const float* __restrict__ w,
                           float eps, int mode, T* __restrict__ out, int n, int groups, long long rows) {
@@ -757,28 +757,66 @@ gated_rmsnorm_warp_kernel(const float* __restrict__ y, const T* __restrict__ gat
     const int gs = n / groups;
     const float* yr = y + (size_t)t * n + (size_t)g * gs;
     const T* zr = gate + (size_t)t * gate_stride + gate_off + (size_t)g * gs;
+    const float* wr = w + (size_t)g * gs;
+    T* o = out + (size_t)t * n + (size_t)g * gs;
     constexpr int kPer = kWarpGroup / 32;
     float v[kPer], zz[kPer];
     float ss = 0.0f;
+    // kVec4 (every row and group starts at a multiple of four elements): a lane takes four neighbouring elements at a time
+    // with one load each of y and of the gate; otherwise one element at a time, a warp's 32 side by side
+    constexpr int kStep = kVec4 ? 4 : 1;
 #pragma unroll
-    for (int i = 0; i < kPer; ++i) {
-        const int j = lane + 32 * i;
-        v[i] = j < gs ? yr[j] : 0.0f;
-        zz[i] = j < gs ? to_float(zr[j]) : 0.0f;
-        if (mode == 0) v[i] *= silu_f(zz[i]);
-        ss += v[i] * v[i];
+    for (int i = 0; i < kPer; i += kStep) {
+        const int j = kVec4 ? 4 * lane + 32 * i : lane + 32 * i;
+        if constexpr (kVec4) {
+            if (j < gs) {
+                const float4 a = *reinterpret_cast<const float4*>(yr + j);
+                v[i] = a.x; v[i + 1] = a.y; v[i + 2] = a.z; v[i + 3] = a.w;
+                if constexpr (sizeof(T) == 2) {
+                    const uint2 b = *reinterpret_cast<const uint2*>(zr + j);
+                    zz[i] = __uint_as_float(b.x << 16); zz[i + 1] = __uint_as_float(b.x & 0xffff0000u);
+                    zz[i + 2] = __uint_as_float(b.y << 16); zz[i + 3] = __uint_as_float(b.y & 0xffff0000u);
+                } else {
+                    const float4 b = *reinterpret_cast<const float4*>(zr + j);
+                    zz[i] = b.x; zz[i + 1] = b.y; zz[i + 2] = b.z; zz[i + 3] = b.w;
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) v[i + q] = zz[i + q] = 0.0f;
+            }
+        } else {
+            v[i] = j < gs ? yr[j] : 0.0f;
+            zz[i] = j < gs ? to_float(zr[j]) : 0.0f;
+        }
+#pragma unroll
+        for (int q = 0; q < kStep; ++q) {
+            if (mode == 0) v[i + q] *= silu_f(zz[i + q]);
+            ss += v[i + q] * v[i + q];
+        }
     }
     ss = warp_sum(ss);
     const float rinv = 1.0f / sqrtf(ss / (float)gs + eps);
-    T* o = out + (size_t)t * n + (size_t)g * gs;
 #pragma unroll
-    for (int i = 0; i < kPer; ++i) {
-        const int j = lane + 32 * i;
+    for (int i = 0; i < kPer; i += kStep) {
+        const int j = kVec4 ? 4 * lane + 32 * i : lane + 32 * i;
         if (j >= gs) break;
-        float u = v[i] * rinv * w[g * gs + j];
-        if (mode == 1) u *= sigmoid_f(zz[i]);
-        else if (mode == 2) u *= silu_f(zz[i]);
-        o[j] = from_float<T>(u);
+        float u[kStep];
+#pragma unroll
+        for (int q = 0; q < kStep; ++q) {
+            u[q] = v[i + q] * rinv * wr[j + q];
+            if (mode == 1) u[q] *= sigmoid_f(zz[i + q]);
+            else if (mode == 2) u[q] *= silu_f(zz[i + q]);
+        }
+        if constexpr (kVec4) {
+            if constexpr (sizeof(T) == 2) {
+                __nv_bfloat162 pk[2] = {__floats2bfloat162_rn(u[0], u[1]), __floats2bfloat162_rn(u[2], u[3])};
+                *reinterpret_cast<uint2*>(o + j) = *reinterpret_cast<const uint2*>(pk);
+            } else {
+                *reinterpret_cast<float4*>(o + j) = make_float4(u[0], u[1], u[2], u[3]);
+            }
+        } else {
+            o[j] = from_float<T>(u[0]);
+        }
     }
 }
 
@@ -1034,12 +1072,18 @@ LI_EXPORT int li_gated_rmsnorm(const float* y, const void* gate, int dtype, int 
     cudaError_t e;
     if (n / groups <= kWarpGroup && (dtype == LI_F32 || dtype == LI_BF16)) {
         const dim3 grid((unsigned)((blocks + 7) / 8));
-        if (dtype == LI_F32)
-            e = li_launch_pdl(gated_rmsnorm_warp_kernel<float>, grid, dim3(256), 0, stream, y, (const float*)gate, gate_stride, gate_off, w, eps, mode,
-                              (float*)out, n, groups, blocks);
-        else
-            e = li_launch_pdl(gated_rmsnorm_warp_kernel<bf16>, grid, dim3(256), 0, stream, y, (const bf16*)gate, gate_stride, gate_off, w, eps, mode,
-                              (bf16*)out, n, groups, blocks);
+        const int gsz = n / groups;
+        const bool vec4 = gsz % 4 == 0 && gate_stride % 4 == 0 && gate_off % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)gate % 16 == 0 &&
+                          (uintptr_t)out % 16 == 0;
+#define LI_NORM(TT, VV)                                                                                                                        \
+    e = li_launch_pdl(gated_rmsnorm_warp_kernel<TT, VV>, grid, dim3(256), 0, stream, y, (const TT*)gate, gate_stride, gate_off, w, eps, mode, (TT*)out, n, \
+                      groups, blocks)
+        if (dtype == LI_F32) {
+            if (vec4) LI_NORM(float, true); else LI_NORM(float, false);
+        } else {
+            if (vec4) LI_NORM(bf16, true); else LI_NORM(bf16, false);
+        }
+#undef LI_NORM
         if (e != cudaSuccess) return li_fail("gated_rmsnorm: launch failed: %s", cudaGetErrorString(e));
         return li_check_launch("gated_rmsnorm");
     }

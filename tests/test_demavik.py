@@ -615,7 +615,7 @@ def test_selective_scan_with_a_state_row_per_channel_kernel(inner, N, rank, dtyp
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,groups,size", [(37, 3, 24), (9, 12, 128), (5, 2, 512), (5, 2, 513), (3, 1, 1200), (70, 1, 1)])
+@pytest.mark.parametrize("T,groups,size", [(37, 3, 24), (9, 12, 128), (5, 2, 512), (5, 2, 513), (3, 1, 1200), (70, 1, 1), (6, 5, 300), (11, 7, 6)])
 def test_gated_norm_kernel_in_short_and_long_groups(T, groups, size, dtype):
     """Groups of up to 512 elements are normed by a warp each, longer ones by a block: both against the plain reference,
     with the gate before the norm and (as a sigmoid or a silu) after it."""
@@ -626,13 +626,15 @@ def test_gated_norm_kernel_in_short_and_long_groups(T, groups, size, dtype):
     torch.manual_seed(T + size)
     n = groups * size
     y32 = torch.randn(T, n, device=dev) * 3.0
-    gate = torch.randn(T, n + 11, device=dev).to(dt)
     w = (1.0 + 0.3 * torch.randn(n, device=dev))
-    for first, act in ((True, "sigmoid"), (False, "sigmoid"), (False, "silu")):
-        a, b = (torch.empty(T, n, device=dev, dtype=dt) for _ in range(2))
-        K.gated_rmsnorm(y32, gate, 5, w, 1e-5, groups, first, a, gate_act=act)
-        R.gated_rmsnorm(y32, gate, 5, w, 1e-5, groups, first, b, gate_act=act)
-        _close(a, b, dtype, f"gated norm, gate first {first}, {act}")
+    # the gate at a column and in rows that are multiples of four elements (loads of four at a time) and that are not
+    for pad, col in ((12, 8), (11, 5)):
+        gate = torch.randn(T, n + pad, device=dev).to(dt)
+        for first, act in ((True, "sigmoid"), (False, "sigmoid"), (False, "silu")):
+            a, b = (torch.empty(T, n, device=dev, dtype=dt) for _ in range(2))
+            K.gated_rmsnorm(y32, gate, col, w, 1e-5, groups, first, a, gate_act=act)
+            R.gated_rmsnorm(y32, gate, col, w, 1e-5, groups, first, b, gate_act=act)
+            _close(a, b, dtype, f"gated norm, gate first {first}, {act}, gate at column {col}")
 
 
 @pytest.mark.gpu
