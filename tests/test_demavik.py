@@ -708,6 +708,24 @@ def test_norm_over_the_whole_projection_rotation_and_cache_write_kernel(dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,ld,ranges", [(37, 56, [(8, 24, 20), (32, 16, 16)]), (19, 50, [(3, 20, 20), (25, 13, 11)]), (5, 4096, [(0, 3072, 3072), (3072, 512, 500)]),
+                                         (9, 64, [(16, 48, 40)])])
+def test_factors_of_a_norm_over_ranges_of_columns_kernel(T, ld, ranges, dtype):
+    """Rows, ranges and columns that are multiples of a 16-byte load (a warp per token) and that are not (a block per token)."""
+    import kernel_refs as R
+    from litinfer_b200 import kernels as K
+
+    dev, dt = torch.device("cuda:0"), _dt(dtype)
+    torch.manual_seed(T + ld)
+    x = (2.0 * torch.randn(T, ld, device=dev)).to(dt)
+    a, b = (torch.zeros(T, 2, device=dev) for _ in range(2))
+    K.row_rinv(x, ranges, 1e-5, a)
+    R.row_rinv(x, ranges, 1e-5, b)
+    _close(a[:, :len(ranges)], b[:, :len(ranges)], "float32", "factors", 1e-5)
+
+
+@pytest.mark.gpu
 def test_routing_by_the_softmax_over_the_chosen_logits_kernel():
     import kernel_refs as R
     from litinfer_b200 import kernels as K
