@@ -1,6 +1,7 @@
 from .demavik import DemavikConfig
 from .filasun import FilasunConfig
 from .gorulorn import GorulornConfig
+from .pifazen import PifazenConfig
 from .qwen2 import ConfigError, Qwen2Config
 from .registry import (
     config_class_for,
@@ -20,6 +21,7 @@ __all__ = [
     "GorulornConfig",
     "ModelSpec",
     "PartSpec",
+    "PifazenConfig",
     "Qwen2Config",
     "ScheduleEntry",
     "config_class_for",

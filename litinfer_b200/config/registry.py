@@ -16,6 +16,7 @@ from typing import Any, Dict, Mapping, Type
 from .demavik import DemavikConfig
 from .filasun import FilasunConfig
 from .gorulorn import GorulornConfig
+from .pifazen import PifazenConfig
 from .qwen2 import ConfigError, Qwen2Config
 from .spec import ModelSpec
 
@@ -85,3 +86,4 @@ register_architecture(Qwen2Config.ARCHITECTURE, Qwen2Config)
 register_architecture(FilasunConfig.ARCHITECTURE, FilasunConfig)
 register_architecture(GorulornConfig.ARCHITECTURE, GorulornConfig)
 register_architecture(DemavikConfig.ARCHITECTURE, DemavikConfig)
+register_architecture(PifazenConfig.ARCHITECTURE, PifazenConfig)

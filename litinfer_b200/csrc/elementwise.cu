@@ -403,6 +403,96 @@ LI_EXPORT int li_glu_clamped(const void* gate_up, void* out, int dtype, int T, i
     return li_check_launch("glu_clamped");
 }
 
+// PolyNorm and a sigmoid gate.
+//   li_polynorm: per token row z [n]: out = a N(z) + b N(z^2) + c N(z^3) + e with powers element by element and
+//     N(v) = v / sqrt(mean(v^2) + eps); coef = {a, b, c, e} float on the device.  The three means are taken in one pass (the row
+//     in registers up to 8,192 elements, else read again), everything in float, one rounding.
+//   li_mul_sigmoid: x[t, i] *= sigmoid(gate[t, gate_off + i / group]) in float, one rounding (an output gate per element, or
+//     with group = a head's width one per head).
+namespace {
+constexpr int kPolyRegs = 8;
+
+template <typename T>
+__global__ void polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps, T* __restrict__ out, int n) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* row = z + (size_t)blockIdx.x * n;
+    T* dst = out + (size_t)blockIdx.x * n;
+    const bool held = n <= kPolyRegs * (int)blockDim.x;
+    float v[kPolyRegs];
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    if (held) {
+#pragma unroll
+        for (int k = 0; k < kPolyRegs; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            v[k] = i < n ? to_float(row[i]) : 0.0f;
+            const float p2 = v[k] * v[k];
+            s2 += p2; s4 = fmaf(p2, p2, s4); s6 = fmaf(p2 * p2, p2, s6);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float x = to_float(row[i]), p2 = x * x;
+            s2 += p2; s4 = fmaf(p2, p2, s4); s6 = fmaf(p2 * p2, p2, s6);
+        }
+    }
+    s2 = block_sum(s2, scratch); s4 = block_sum(s4, scratch); s6 = block_sum(s6, scratch);
+    const float inv_n = 1.0f / (float)n;
+    const float a = coef[0] / sqrtf(s2 * inv_n + eps), b = coef[1] / sqrtf(s4 * inv_n + eps), c = coef[2] / sqrtf(s6 * inv_n + eps), e = coef[3];
+    if (held) {
+#pragma unroll
+        for (int k = 0; k < kPolyRegs; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < n) dst[i] = from_float<T>(fmaf(v[k], fmaf(v[k], fmaf(v[k], c, b), a), e));
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float x = to_float(row[i]);
+            dst[i] = from_float<T>(fmaf(x, fmaf(x, fmaf(x, c, b), a), e));
+        }
+    }
+}
+
+template <typename T>
+__global__ void mul_sigmoid_kernel(T* __restrict__ x, const T* __restrict__ gate, int gate_stride, int gate_off, int group, int n, long long total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const long long t = i / n;
+        const int j = (int)(i - t * n);
+        const float g = to_float(gate[t * gate_stride + gate_off + j / group]);
+        x[i] = from_float<T>(to_float(x[i]) / (1.0f + expf(-g)));
+    }
+}
+}  // namespace
+
+LI_EXPORT int li_polynorm(const void* z, int dtype, const float* coef, float eps, void* out, int T, int n, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && n > 0 && coef != nullptr, "polynorm: bad sizes T=%d n=%d", T, n);
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "polynorm: unknown dtype %d", dtype);
+    if (T == 0) return 0;
+    int threads = ((ceil_div(n, kPolyRegs) + 31) / 32) * 32;
+    threads = threads < 64 ? 64 : threads > 1024 ? 1024 : threads;
+    cudaError_t e;
+    if (dtype == LI_F32) e = li_launch_pdl(polynorm_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)z, coef, eps, (float*)out, n);
+    else e = li_launch_pdl(polynorm_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)z, coef, eps, (bf16*)out, n);
+    if (e != cudaSuccess) return li_fail("polynorm: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("polynorm");
+}
+
+LI_EXPORT int li_mul_sigmoid(void* x, const void* gate, int dtype, int gate_stride, int gate_off, int group, int T, int n, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && n > 0 && group > 0 && n % group == 0 && gate_off >= 0 && gate_off + n / group <= gate_stride, "mul_sigmoid: bad sizes T=%d n=%d (gate at %d of %d)", T, n, gate_off, gate_stride);
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "mul_sigmoid: unknown dtype %d", dtype);
+    const long long total = (long long)T * n;
+    if (total == 0) return 0;
+    cudaError_t e;
+    if (dtype == LI_F32) e = li_launch_pdl(mul_sigmoid_kernel<float>, dim3(grid_for(total, 256)), dim3(256), 0, stream, (float*)x, (const float*)gate, gate_stride, gate_off, group, n, total);
+    else e = li_launch_pdl(mul_sigmoid_kernel<bf16>, dim3(grid_for(total, 256)), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate, gate_stride, gate_off, group, n, total);
+    if (e != cudaSuccess) return li_fail("mul_sigmoid: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("mul_sigmoid");
+}
+
 // out[tok, :] = hprime[tok, :] / sqrt(sum of ssq[:, tok] / width + eps): the normalised activation itself, for a
 // consumer that cannot take the factor into its own product (row_scale.cuh).  bfloat16.
 namespace {

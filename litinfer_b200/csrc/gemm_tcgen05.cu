@@ -610,15 +610,20 @@ int li_linear_tcgen05_rope(const void* a, const void* w, const float* bias, void
 }
 
 // Products in groups: a [M, K] with M a multiple of 128, every tile of 128 rows the rows of one group (tile_group[tile], -1: none);
-// w [G, N, K]; out [M, N] in bfloat16, or [M, N / 2] with swiglu (gate and up rows of every group interleaved in eights).
+// w [G, N, K]; out [M, N] in bfloat16, or [M, N / 2] with a gated epilogue (gate and up rows of every group interleaved in eights).
 // Tiles of 128 x 256 (wide products) or 128 x 128, one CTA each.
-int li_linear_tcgen05_grouped(const void* a, const void* w, void* out, int M, int N, int K, int G, const int* tile_group, int swiglu,
-                              cudaStream_t stream) {
+int li_linear_tcgen05_grouped(const void* a, const void* w, void* out, int M, int N, int K, int G, const int* tile_group, int epilogue,
+                              const float* glu_params, cudaStream_t stream) {
     LI_REQUIRE(M % 128 == 0 && G >= 1 && tile_group != nullptr, "grouped linear (tcgen05): rows %d must be whole tiles of 128 with a table of their groups", M);
     LI_REQUIRE(K >= 8 && K % 8 == 0 && ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "grouped linear (tcgen05): refuses K=%d or unaligned operands", K);
-    LI_REQUIRE(!swiglu || N % 16 == 0, "grouped linear (tcgen05): the swiglu epilogue needs N a multiple of 16, got %d", N);
+    const bool gated = li_epilogue_is_gated(epilogue);
+    LI_REQUIRE(!gated || N % 16 == 0, "grouped linear (tcgen05): a gated epilogue needs N a multiple of 16, got %d", N);
     const bool wide = N >= 1024;
-    if (swiglu)
+    // (a gated product has no bias: the bounded unit's parameters travel in its place, as in the plain products)
+    if (epilogue == LI_EPILOGUE_GLU_CLAMPED)
+        return wide ? launch_tile<128, 256, bf16, 2>(a, w, glu_params, out, M, N, K, stream, 1, RopeEpilogue{}, tile_group, G)
+                    : launch_tile<128, 128, bf16, 2>(a, w, glu_params, out, M, N, K, stream, 1, RopeEpilogue{}, tile_group, G);
+    if (gated)
         return wide ? launch_tile<128, 256, bf16, 1>(a, w, nullptr, out, M, N, K, stream, 1, RopeEpilogue{}, tile_group, G)
                     : launch_tile<128, 128, bf16, 1>(a, w, nullptr, out, M, N, K, stream, 1, RopeEpilogue{}, tile_group, G);
     return wide ? launch_tile<128, 256, bf16, 0>(a, w, nullptr, out, M, N, K, stream, 1, RopeEpilogue{}, tile_group, G)

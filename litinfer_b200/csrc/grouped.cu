@@ -126,12 +126,13 @@ __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1
 // TM 64: many rows a group (portions of prompts); a warp takes 16 rows and all 64 columns.  TM 16: few rows a group
 // (single tokens: the weights are what is read): a warp takes all 16 rows and 16 of the columns, and four stages of
 // 64 elements keep more of the weights on their way.
-// kSwiglu: the columns come as 8 gate, 8 up, 8 gate, 8 up, ... (the rows of every group's matrix interleaved in eights), and
-// out [M, N / 2] takes up * gate / (1 + exp(-gate)): a thread holds a gate column and its up column in neighbouring tiles of 8.
-template <int TM, int TK, int ST, bool kSwiglu>
+// kSwiglu (1, or 2: the gated unit with bounded operands, glu_params = {limit, alpha} on the device): the columns come as 8 gate,
+// 8 up, 8 gate, 8 up, ... (the rows of every group's matrix interleaved in eights), and out [M, N / 2] takes
+// up * gate / (1 + exp(-gate)) (or the bounded unit): a thread holds a gate column and its up column in neighbouring tiles of 8.
+template <int TM, int TK, int ST, int kSwiglu>
 __global__ void __launch_bounds__(128)
 grouped_mma_kernel(const bf16* __restrict__ A, int lda, int a_gcol, const bf16* __restrict__ W, bf16* __restrict__ C, int ldc, int c_gcol,
-                   const int* __restrict__ row_offsets, int M, int N, int K, int G) {
+                   const int* __restrict__ row_offsets, int M, int N, int K, int G, const float* __restrict__ glu_params) {
     __shared__ __align__(16) bf16 As[ST][TM][TK + MPAD];
     __shared__ __align__(16) bf16 Ws[ST][BN][TK + MPAD];
     pdl_launch_dependents();
@@ -214,8 +215,8 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, int a_gcol, const bf16* 
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 if (gate_col + i + 8 < N) {
-                    if (r_lo < m_end) c[(size_t)r_lo * ldc + n + i] = __float2bfloat16_rn(swiglu_of<bf16>(acc[j][i], acc[j + 1][i]));
-                    if (r_hi < m_end) c[(size_t)r_hi * ldc + n + i] = __float2bfloat16_rn(swiglu_of<bf16>(acc[j][2 + i], acc[j + 1][2 + i]));
+                    if (r_lo < m_end) c[(size_t)r_lo * ldc + n + i] = __float2bfloat16_rn(glu_of<bf16, kSwiglu == 2>(acc[j][i], acc[j + 1][i], glu_params));
+                    if (r_hi < m_end) c[(size_t)r_hi * ldc + n + i] = __float2bfloat16_rn(glu_of<bf16, kSwiglu == 2>(acc[j][2 + i], acc[j + 1][2 + i], glu_params));
                 }
             }
         }
@@ -288,10 +289,109 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int scoring, 
     }
 }
 
+// Routing over all experts at once with groups: scores s = softmax(logits) over the E outputs; the choice scores are
+// s + correction; the experts form `groups` equal groups of neighbours, a group's score is its largest choice score, and only
+// experts of the `keep` best groups can be chosen (the lower index wins a tie, among groups and among experts); the `top`
+// largest choice scores choose; the weights are the chosen experts' s (without the correction), divided by their sum + 1e-20,
+// times `scale`.  One warp a token, everything in float.
+__global__ void moe_route_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int T, int E, int top, int groups,
+                                         int keep, float scale, int* __restrict__ ids, float* __restrict__ weights) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float s[kMaxExpertsPerLane], c[kMaxExpertsPerLane];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+        const int e = lane + 32 * i;
+        s[i] = e < E ? logits[(size_t)t * E + e] : -INFINITY;
+        m = fmaxf(m, s[i]);
+    }
+    m = warp_max(m);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+        s[i] = lane + 32 * i < E ? expf(s[i] - m) : 0.0f;
+        sum += s[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+        const int e = lane + 32 * i;
+        s[i] = s[i] / sum;
+        c[i] = e < E ? s[i] + (correction ? correction[e] : 0.0f) : -INFINITY;
+    }
+    const int per = E / groups;
+    if (keep < groups) {
+        // the groups' scores, then `keep` rounds that each take the best group left; an expert stays if its group was taken
+        unsigned taken[kMaxExpertsPerLane];                     // per expert of this lane: its group is among the kept ones
+#pragma unroll
+        for (int i = 0; i < kMaxExpertsPerLane; ++i) taken[i] = 0u;
+        for (int round = 0; round < keep; ++round) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+                const int e = lane + 32 * i;
+                if (e < E && !taken[i]) {
+                    const int g = e / per;
+                    if (c[i] > best || (c[i] == best && g < arg)) best = c[i], arg = g;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
+            }
+#pragma unroll
+            for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+                const int e = lane + 32 * i;
+                if (e < E && e / per == arg) taken[i] = 1u;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxExpertsPerLane; ++i)
+            if (!taken[i]) c[i] = -INFINITY;
+    }
+    float wsum = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY, score = 0.0f;
+        int arg = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && (c[i] > best || (arg == 0x7fffffff && c[i] == best))) best = c[i], arg = e, score = s[i];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            const float os = __shfl_xor_sync(0xffffffffu, score, o);
+            if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa, score = os;
+        }
+        if (lane == 0) {
+            ids[(size_t)t * top + k] = arg;
+            weights[(size_t)t * top + k] = score;
+        }
+        wsum += score;
+#pragma unroll
+        for (int i = 0; i < kMaxExpertsPerLane; ++i)
+            if (lane + 32 * i == arg) c[i] = -INFINITY, s[i] = 0.0f;
+    }
+    if (lane == 0) {
+        float* wt = weights + (size_t)t * top;
+        for (int k = 0; k < top; ++k) wt[k] = wt[k] / (wsum + 1e-20f) * scale;
+    }
+}
+
 // One block per expert.  n pairs (token, choice) in order; ids[i] is pair i's expert.  Every expert's run of rows starts
 // at a multiple of `pad` (1: runs follow one another closely); the places between a run's last pair and the next run
 // hold no pair (-1).  tile_group (may be NULL; pad > 1): for every tile of `pad` rows, the expert it belongs to, -1 behind the last run.
-__global__ void moe_sort_kernel(const int* __restrict__ ids, int n, int E, int pad, int* __restrict__ offsets, int* __restrict__ pair_at,
+// Experts from `matrices` on have no matrices (their rows pass as they are): their tiles belong to no group either (-1).
+__global__ void moe_sort_kernel(const int* __restrict__ ids, int n, int E, int matrices, int pad, int* __restrict__ offsets, int* __restrict__ pair_at,
                                 int* __restrict__ place_of, int* __restrict__ tile_group, int n_tiles, int places) {
     __shared__ int warp_total[32];
     __shared__ int hist[kMaxExpertsPerLane * 32];
@@ -339,7 +439,7 @@ __global__ void moe_sort_kernel(const int* __restrict__ ids, int n, int E, int p
     if (e == E - 1)
         for (int r = end + threadIdx.x; r < places; r += blockDim.x) pair_at[r] = -1;          // places behind the last run belong to nobody
     if (tile_group != nullptr) {
-        for (int tl = start / pad + threadIdx.x; tl < end / pad && tl < n_tiles; tl += blockDim.x) tile_group[tl] = e;
+        for (int tl = start / pad + threadIdx.x; tl < end / pad && tl < n_tiles; tl += blockDim.x) tile_group[tl] = e < matrices ? e : -1;
         if (e == E - 1)
             for (int tl = end / pad + threadIdx.x; tl < n_tiles; tl += blockDim.x) tile_group[tl] = -1;
     }
@@ -388,20 +488,24 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
 
 }  // namespace
 
-int li_linear_tcgen05_grouped(const void* a, const void* w, void* out, int M, int N, int K, int G, const int* tile_group, int swiglu,
-                              cudaStream_t stream);
+int li_linear_tcgen05_grouped(const void* a, const void* w, void* out, int M, int N, int K, int G, const int* tile_group, int epilogue,
+                              const float* glu_params, cudaStream_t stream);
 
 // tile_group (may be NULL; rows in groups whose runs start at multiples of 128, li_moe_sort with pad 128): the group of
 // every tile of 128 rows; bfloat16 products of at least kTensorRows rows then run on tcgen05 tiles.
 constexpr int kTensorRows = 256;
 
-// epilogue: LI_EPILOGUE_NONE, or LI_EPILOGUE_SWIGLU (bfloat16, K a multiple of 8, N a multiple of 16): gate and up rows of
-// every group's matrix interleaved in eights, out rows of N / 2 activations.
+// epilogue: LI_EPILOGUE_NONE, or a gated one (bfloat16, K a multiple of 8, N a multiple of 16): gate and up rows of
+// every group's matrix interleaved in eights, out rows of N / 2 activations; LI_EPILOGUE_GLU_CLAMPED reads its {limit, alpha}
+// from glu_params on the device.
 LI_EXPORT int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets,
-                                const int* tile_group, int dtype, int M, int N, int K, int G, int epilogue, cudaStream_t stream) {
+                                const int* tile_group, int dtype, int M, int N, int K, int G, int epilogue, const float* glu_params,
+                                cudaStream_t stream) {
     LI_REQUIRE(M >= 0 && N > 0 && K > 0 && G > 0, "grouped_linear: bad sizes M=%d N=%d K=%d G=%d", M, N, K, G);
-    LI_REQUIRE(epilogue == LI_EPILOGUE_NONE || epilogue == LI_EPILOGUE_SWIGLU, "grouped_linear: unknown epilogue %d", epilogue);
-    const bool swiglu = epilogue == LI_EPILOGUE_SWIGLU;
+    LI_REQUIRE(epilogue == LI_EPILOGUE_NONE || li_epilogue_is_gated(epilogue), "grouped_linear: unknown epilogue %d", epilogue);
+    LI_REQUIRE(li_epilogue_bias_ok(epilogue, glu_params) || epilogue == LI_EPILOGUE_NONE, "grouped_linear: the bounded unit needs its parameters, the others take none");
+    const bool swiglu = li_epilogue_is_gated(epilogue);
+    const bool clamped = epilogue == LI_EPILOGUE_GLU_CLAMPED;
     const int out_cols = swiglu ? N / 2 : N;
     LI_REQUIRE(lda >= K && ldc >= out_cols, "grouped_linear: rows of %d and %d elements cannot hold K=%d and %d outputs", lda, ldc, K, out_cols);
     LI_REQUIRE(row_offsets == nullptr || (a_gcol == 0 && c_gcol == 0), "grouped_linear: groups are rows or columns, not both");
@@ -409,7 +513,7 @@ LI_EXPORT int li_grouped_linear(const void* a, int lda, int a_gcol, const void* 
     if (M == 0) return 0;
     if (dtype == LI_BF16 && row_offsets != nullptr && tile_group != nullptr && M >= kTensorRows && M % 128 == 0 && lda == K && ldc == out_cols &&
         K % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0 && (!swiglu || N % 16 == 0))
-        return li_linear_tcgen05_grouped(a, w, out, M, N, K, G, tile_group, swiglu ? 1 : 0, stream);
+        return li_linear_tcgen05_grouped(a, w, out, M, N, K, G, tile_group, epilogue, glu_params, stream);
     const int row_tiles = ceil_div(M, BM);
     const dim3 grid(ceil_div(N, BN), row_offsets ? row_tiles + G : row_tiles, row_offsets ? 1 : G);
     LI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "grouped_linear: too many tiles for one launch");
@@ -422,15 +526,13 @@ LI_EXPORT int li_grouped_linear(const void* a, int lda, int a_gcol, const void* 
     if (dtype == LI_BF16 && aligned && few) {
         const int tiles16 = ceil_div(M, 16);
         const dim3 grid16(ceil_div(N, BN), row_offsets ? tiles16 + G : tiles16, row_offsets ? 1 : G);
-        e = swiglu ? li_launch_pdl(grouped_mma_kernel<16, 64, 4, true>, grid16, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w,
-                                   (bf16*)out, ldc, c_gcol, row_offsets, M, N, K, G)
-                   : li_launch_pdl(grouped_mma_kernel<16, 64, 4, false>, grid16, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w,
-                                   (bf16*)out, ldc, c_gcol, row_offsets, M, N, K, G);
+#define LI_GROUPED_MMA(TM_, TK_, ST_, EPI_, GRID_)                                                                                          \
+    li_launch_pdl(grouped_mma_kernel<TM_, TK_, ST_, EPI_>, GRID_, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w, (bf16*)out, ldc, \
+                  c_gcol, row_offsets, M, N, K, G, glu_params)
+        e = clamped ? LI_GROUPED_MMA(16, 64, 4, 2, grid16) : swiglu ? LI_GROUPED_MMA(16, 64, 4, 1, grid16) : LI_GROUPED_MMA(16, 64, 4, 0, grid16);
     } else if (dtype == LI_BF16 && aligned)
-        e = swiglu ? li_launch_pdl(grouped_mma_kernel<64, 32, 3, true>, grid, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w,
-                                   (bf16*)out, ldc, c_gcol, row_offsets, M, N, K, G)
-                   : li_launch_pdl(grouped_mma_kernel<64, 32, 3, false>, grid, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w,
-                                   (bf16*)out, ldc, c_gcol, row_offsets, M, N, K, G);
+        e = clamped ? LI_GROUPED_MMA(64, 32, 3, 2, grid) : swiglu ? LI_GROUPED_MMA(64, 32, 3, 1, grid) : LI_GROUPED_MMA(64, 32, 3, 0, grid);
+#undef LI_GROUPED_MMA
     else if (dtype == LI_F32)
         e = li_launch_pdl(grouped_linear_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)a, lda, a_gcol, (const float*)w, (float*)out,
                           ldc, c_gcol, row_offsets, M, N, K, G);
@@ -453,14 +555,29 @@ LI_EXPORT int li_moe_route(const float* logits, int scoring, int T, int E, int t
     return li_check_launch("moe_route");
 }
 
+// See moe_route_grouped_kernel.  correction (may be NULL): [E] float; groups divides E; 1 <= keep <= groups; the kept groups
+// must hold at least `top` experts.
+LI_EXPORT int li_moe_route_grouped(const float* logits, const float* correction, int T, int E, int top, int groups, int keep, float scale, int* ids,
+                                   float* weights, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && E > 0 && top > 0 && top <= E, "moe_route_grouped: %d of %d experts", top, E);
+    LI_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups && keep * (E / groups) >= top,
+               "moe_route_grouped: %d of %d groups of %d experts cannot give %d choices", keep, groups, groups >= 1 ? E / groups : 0, top);
+    LI_REQUIRE(E <= 32 * kMaxExpertsPerLane, "moe_route_grouped: %d experts are more than %d", E, 32 * kMaxExpertsPerLane);
+    if (T == 0) return 0;
+    const cudaError_t e = li_launch_pdl(moe_route_grouped_kernel, dim3(ceil_div(T, 4)), dim3(128), 0, stream, logits, correction, T, E, top, groups, keep,
+                                        scale, ids, weights);
+    if (e != cudaSuccess) return li_fail("moe_route_grouped: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("moe_route_grouped");
+}
+
 // pad: every expert's run of rows starts at a multiple of it; pair_at has `places` entries, room for n + E (pad - 1) of them,
 // and tile_group (may be NULL) one entry for each of its n_tiles tiles of pad rows.
-LI_EXPORT int li_moe_sort(const int* ids, int n, int E, int pad, int* offsets, int* pair_at, int* place_of, int* tile_group, int n_tiles,
+LI_EXPORT int li_moe_sort(const int* ids, int n, int E, int matrices, int pad, int* offsets, int* pair_at, int* place_of, int* tile_group, int n_tiles,
                           int places, cudaStream_t stream) {
-    LI_REQUIRE(n >= 0 && E > 0 && pad >= 1, "moe_sort: bad sizes");
+    LI_REQUIRE(n >= 0 && E > 0 && pad >= 1 && matrices >= 0 && matrices <= E, "moe_sort: bad sizes");
     LI_REQUIRE(places >= n + (pad > 1 ? E * (pad - 1) : 0), "moe_sort: %d places cannot hold %d pairs in runs padded to %d", places, n, pad);
     LI_REQUIRE(E <= 32 * kMaxExpertsPerLane, "moe_sort: %d experts are more than %d", E, 32 * kMaxExpertsPerLane);
-    const cudaError_t e = li_launch_pdl(moe_sort_kernel, dim3(E), dim3(256), 0, stream, ids, n, E, pad, offsets, pair_at, place_of, tile_group, n_tiles, places);
+    const cudaError_t e = li_launch_pdl(moe_sort_kernel, dim3(E), dim3(256), 0, stream, ids, n, E, matrices, pad, offsets, pair_at, place_of, tile_group, n_tiles, places);
     if (e != cudaSuccess) return li_fail("moe_sort: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("moe_sort");
 }

@@ -109,6 +109,13 @@ int li_apply_row_scale(const void* hprime, const float* ssq, int nparts, int wid
  * [T, 2 I] as gate | up. */
 int li_glu_clamped(const void* gate_up, void* out, int dtype, int T, int I, float limit, float alpha, cudaStream_t stream);
 
+/* out = a N(z) + b N(z^2) + c N(z^3) + e per row of z [T, n], powers element by element, N(v) = v / sqrt(mean(v^2) + eps),
+ * coef = {a, b, c, e} float on the device. */
+int li_polynorm(const void* z, int dtype, const float* coef, float eps, void* out, int T, int n, cudaStream_t stream);
+
+/* x [T, n] *= sigmoid(gate [T, gate_stride] at column gate_off + i / group), in float, one rounding. */
+int li_mul_sigmoid(void* x, const void* gate, int dtype, int gate_stride, int gate_off, int group, int T, int n, cudaStream_t stream);
+
 /* out = sa a + sb b over n elements of the run dtype (the sum in float). */
 int li_weighted_sum2(const void* a, const void* b, float sa, float sb, void* out, int dtype, long long n, cudaStream_t stream);
 
@@ -166,6 +173,15 @@ int li_scan_carry(float* state, long long state_stride, float* chunk_state, cons
 int li_gla_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const float* za, int za_stride, int za_off,
     float inv_tau, float q_scale, float* state, long long state_stride, const int* q_start, const int* slots, float* out,
     int S, int heads, int d, int dv, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream);
+
+/* Per head S [d, dv] under the gated delta rule: S = diag(g) S, u = beta (v - S^T k), S = S + k u^T, out = S^T q.  q and k
+ * (kv_heads of them, head h uses h / (heads / kv_heads)) at q_off, k_off of qkv [T, stride], made unit vectors here
+ * (x / sqrt(sum x^2 + unit_eps), q times q_scale); v (heads x dv) at v_off; beta = sigmoid(b [T, b_stride] at b_off + h);
+ * g = exp(-exp(A_log[h]) softplus(za [T, za_stride] at za_off + h d + i)), za float; the state is kept as [heads][dv][d]. */
+int li_delta_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const void* b, int b_stride, int b_off,
+    const float* za, int za_stride, int za_off, const float* A_log, float q_scale, float unit_eps, float* state,
+    long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv,
+    cudaStream_t stream);
 
 /* Per channel c a state S [N]: S = exp(dt_c A[c, :]) S + dt_c x_c B, y_c = (S . C + D[c] x_c) silu(z_c), with
  * dt = softplus(dt_raw) (float, [T, dt_stride]), A = -exp(A_log) [inner, N]; x at column x_off of [T, x_stride], B and C
@@ -273,6 +289,14 @@ int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* co
     const float* denom, int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh,
     int page_size, int num_pages, int write, int shift, int to_cache, int out_ld, cudaStream_t stream);
 
+/* Latent attention with a rotated part, per token: c = rmsnorm(low[col_c : col_c + R]) * w into the key and the value head of
+ * out [T, (nh + 2) dl]; the shared key part low[col_r : col_r + dr] rotated behind c in the key head; every query head's
+ * rotated part q[h (d + dr) + d ...] rotated behind the head's first R columns; the rest of the heads zero.  Pair i turns by
+ * float(pos) / denom[i]; interleaved: pair (2i, 2i + 1), else (i, i + dr / 2); cosine and sine times magnitude. */
+int li_latent_rope_post(const void* low, int dtype, int ld_low, int col_c, int col_r, const void* q, int ld_q, int d, const float* w, float eps,
+    const int* positions, const float* denom, float magnitude, int interleaved, void* out, int T, int nh, int R, int dr,
+    int dl, cudaStream_t stream);
+
 /* out[t, j] = 1 / sqrt(sum of squares of the columns col_j .. col_j + n_j - 1 of x [T, ld] / width_j + eps), j = 0, 1 (n_1
  * 0: one range): the factor of an RMS norm over a whole projection, for li_conv_norm_rope_kv's row_rinv. */
 int li_row_rinv(const void* x, int dtype, int ld, int col0, int n0, int width0, int col1, int n1, int width1, float eps, float* out,
@@ -285,15 +309,24 @@ int li_row_rinv(const void* x, int dtype, int ld, int col0, int n0, int width0, 
  * large bfloat16 products then run on tcgen05 tiles.  epilogue 1 (bfloat16): gate and up rows of every matrix interleaved in
  * eights, out rows of N / 2 activations up * gate / (1 + exp(-gate)). */
 int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets,
-    const int* tile_group, int dtype, int M, int N, int K, int G, int epilogue, cudaStream_t stream);
+    const int* tile_group, int dtype, int M, int N, int K, int G, int epilogue, const float* glu_params,
+    cudaStream_t stream);
 
 /* ids, weights [T, top]: the experts with the largest sigmoid(logits [T, E]) and those scores (scoring 0), or the experts
  * with the largest logits and the softmax over the chosen logits alone (scoring 1). */
 int li_moe_route(const float* logits, int scoring, int T, int E, int top, int* ids, float* weights, cudaStream_t stream);
 
+/* The same choice for a router over all experts at once with groups: s = softmax(logits [T, E]); choice scores s + correction
+ * (may be NULL); the experts form `groups` equal groups of neighbours, a group's score is its largest choice score, only the
+ * `keep` best groups' experts can be chosen; the `top` largest choice scores choose; weights = s of the chosen / (their sum +
+ * 1e-20) * scale. */
+int li_moe_route_grouped(const float* logits, const float* correction, int T, int E, int top, int groups, int keep, float scale, int* ids,
+    float* weights, cudaStream_t stream);
+
 /* Stable sort of n (token, choice) pairs by expert: offsets [E + 1], pair_at (pair at a sorted place, -1: none), place_of [n].
- * Every expert's run starts at a multiple of pad; pair_at has `places` entries; tile_group (may be NULL) [n_tiles]: the expert of every tile of pad rows. */
-int li_moe_sort(const int* ids, int n, int E, int pad, int* offsets, int* pair_at, int* place_of, int* tile_group, int n_tiles,
+ * Every expert's run starts at a multiple of pad; pair_at has `places` entries; tile_group (may be NULL) [n_tiles]: the expert of
+ * every tile of pad rows, -1 for the experts from `matrices` on (experts without matrices, whose rows pass as they are). */
+int li_moe_sort(const int* ids, int n, int E, int matrices, int pad, int* offsets, int* pair_at, int* place_of, int* tile_group, int n_tiles,
     int places, cudaStream_t stream);
 
 /* out [n, H]: row r is h[pair_at[r] / top], times weights[pair_at[r]] if weights is given; zeros where pair_at[r] < 0. */

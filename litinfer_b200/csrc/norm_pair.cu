@@ -5,8 +5,8 @@
 //       x += post(y)          post: a norm of the sublayer's output y with its own weight (or none: x += y; or no y at all)
 //       out = next(x)         next: the norm that feeds the following sublayer (optional; without one, out may still be
 //                             asked for and is x in the run dtype: a sublayer that reads the stream itself)
-//     where a norm is  (v - mean) / sqrt(var + eps) * w  (centered: layer norm without bias, var the mean of the squared
-//     deviations) or  v / sqrt(mean(v^2) + eps) * w  (not centered: RMS norm).  Rows may be gathered (rows[r]) when
+//     where a norm is  (v - mean) / sqrt(var + eps) * w  (centered 1: layer norm without bias, var the mean of the squared
+//     deviations),  v / sqrt(mean(v^2) + eps) * w  (centered 0: RMS norm)  or just  v * w  (centered 2: a factor per channel).  Rows may be gathered (rows[r]) when
 //     there is no y: the model's last norm on the wanted rows only.
 //   li_add_row: x[t] += table[row] for every token (a vector per pass of a looped span of layers).
 //   li_rmsnorm_cols: RMS norm of n columns of a run-dtype matrix, written to (up to) two places of another matrix.
@@ -17,6 +17,10 @@
 #include "common.cuh"
 
 namespace {
+
+// what `centered` says of a norm: 0 an RMS norm, 1 a layer norm without bias, 2 no statistic at all: the row times the weight
+// (a learned factor per channel on a sublayer's output)
+constexpr int kScaleOnly = 2;
 
 template <typename T>
 __device__ __forceinline__ float row_stat_norm(const T* __restrict__ v, int H, int centered, float eps, float* scratch, float* mean_out) {
@@ -52,7 +56,9 @@ __global__ void norm_add_norm_kernel(float* __restrict__ x, const T* __restrict_
     float* xr = x + (size_t)src * H;
     if (y) {
         const T* yr = y + (size_t)r * H;
-        if (w_post) {
+        if (w_post && post_centered == kScaleOnly) {
+            for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] += to_float(yr[i]) * w_post[i];
+        } else if (w_post) {
             float mean;
             const float rinv = row_stat_norm(yr, H, post_centered, eps_post, scratch, &mean);
             for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] += (to_float(yr[i]) - mean) * rinv * w_post[i];
@@ -61,7 +67,10 @@ __global__ void norm_add_norm_kernel(float* __restrict__ x, const T* __restrict_
         }
         __syncthreads();                                  // the row's new values are read by other threads below
     }
-    if (w_next) {
+    if (w_next && next_centered == kScaleOnly) {
+        T* o = out + (size_t)r * H;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<T>(xr[i] * w_next[i]);
+    } else if (w_next) {
         float mean;
         const float rinv = row_stat_norm(xr, H, next_centered, eps_next, scratch, &mean);
         T* o = out + (size_t)r * H;
@@ -168,6 +177,13 @@ __device__ __forceinline__ void store_row(bf16* __restrict__ p, const float (&v)
 template <bool kVec>
 __device__ __forceinline__ void row_norm(float (&dst)[kRegs], const float (&v)[kRegs], const float* __restrict__ w, int centered, float eps, int H,
                                          float* scratch) {
+    if (centered == kScaleOnly) {                       // (the same for every thread of the block: no barrier is skipped by some)
+        float wv[kRegs];
+        load_row<kVec>(wv, w, H);
+#pragma unroll
+        for (int k = 0; k < kRegs; ++k) dst[k] = v[k] * wv[k];
+        return;
+    }
     const float inv_h = 1.0f / (float)H;
     float mean = 0.0f;
     if (centered) {

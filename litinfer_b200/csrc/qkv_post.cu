@@ -311,3 +311,87 @@ LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const
     if (e != cudaSuccess) return li_fail("conv_norm_rope_kv: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("conv_norm_rope_kv");
 }
+
+// Latent attention with a rotated part: what stands between its projections and attention over the latent.
+// Per token, with a latent of R and a rotated part of dr elements, heads of the attention dl >= R + dr wide:
+//   * the key/value latent  c = low[col_c : col_c + R] / sqrt(mean(.^2) + eps) * w  goes to the key head's and the value head's
+//     first R columns of the attention row `out` [T, (nh + 2) dl];
+//   * the one rotated key part all heads share, low[col_r : col_r + dr], is rotated and follows c in the key head;
+//   * every query head's rotated part, q[h (d + dr) + d : (h + 1) (d + dr)], is rotated and goes behind the head's first R
+//     columns (which the product that carries the unrotated query into the latent space fills);
+//   * what is left of every head (and of the value head behind c) is set to zero.
+// Rotation: pair i turns by float(pos) / denom[i]; `interleaved`: the pair is (2i, 2i + 1), else (i, i + dr / 2); cosine and
+// sine are multiplied by `magnitude`.  Norm and angles in float, one rounding.  One block per token.
+namespace {
+template <typename T>
+__global__ void latent_rope_post_kernel(const T* __restrict__ low, int ld_low, int col_c, int col_r, const T* __restrict__ q, int ld_q, int d,
+                                        const float* __restrict__ w, float eps, const int* __restrict__ positions, const float* __restrict__ denom,
+                                        float magnitude, int interleaved, T* __restrict__ out, int nh, int R, int dr, int dl) {
+    __shared__ float scratch[32];
+    extern __shared__ float cs[];                       // [dr / 2][2]: cosine and sine of the token's pairs, with the magnitude
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half = dr >> 1;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, c;
+        sincosf(pos / denom[i], &sn, &c);
+        cs[2 * i] = c * magnitude;
+        cs[2 * i + 1] = sn * magnitude;
+    }
+    const T* lrow = low + (size_t)t * ld_low;
+    T* orow = out + (size_t)t * (nh + 2) * dl;
+    float ssq = 0.0f;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+        const float v = to_float(lrow[col_c + i]);
+        ssq = fmaf(v, v, ssq);
+    }
+    ssq = block_sum(ssq, scratch);                      // (its barriers also make the table above visible)
+    const float rinv = 1.0f / sqrtf(ssq / (float)R + eps);
+    T* khead = orow + (size_t)nh * dl;
+    T* vhead = khead + dl;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+        const T c = from_float<T>(to_float(lrow[col_c + i]) * rinv * w[i]);
+        khead[i] = c;
+        vhead[i] = c;
+    }
+    for (int i = R + threadIdx.x; i < dl; i += blockDim.x) vhead[i] = from_float<T>(0.0f);
+    // heads 0 .. nh - 1: the queries' rotated parts; head nh: the key's
+    for (int idx = threadIdx.x; idx < (nh + 1) * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        const T* src = h < nh ? q + (size_t)t * ld_q + (size_t)h * (d + dr) + d : lrow + col_r;
+        T* dst = orow + (size_t)h * dl + R;
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+        const float a = to_float(src[ia]), b = to_float(src[ib]);
+        const float c = cs[2 * i], sn = cs[2 * i + 1];
+        dst[ia] = from_float<T>(a * c - b * sn);
+        dst[ib] = from_float<T>(b * c + a * sn);
+    }
+    const int pad = dl - R - dr;
+    for (int idx = threadIdx.x; idx < (nh + 1) * pad; idx += blockDim.x) {
+        const int h = idx / pad, i = idx - h * pad;
+        orow[(size_t)h * dl + R + dr + i] = from_float<T>(0.0f);
+    }
+}
+}  // namespace
+
+LI_EXPORT int li_latent_rope_post(const void* low, int dtype, int ld_low, int col_c, int col_r, const void* q, int ld_q, int d, const float* w, float eps,
+                                  const int* positions, const float* denom, float magnitude, int interleaved, void* out, int T, int nh, int R, int dr,
+                                  int dl, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && nh > 0 && R > 0 && dr >= 0 && dr % 2 == 0 && dl >= R + dr && d >= 0, "latent_rope_post: bad sizes nh=%d R=%d dr=%d dl=%d", nh, R, dr, dl);
+    LI_REQUIRE(col_c >= 0 && col_c + R <= ld_low && col_r >= 0 && col_r + dr <= ld_low && nh * (d + dr) <= ld_q, "latent_rope_post: columns do not fit the rows");
+    LI_REQUIRE(dr == 0 || denom != nullptr, "latent_rope_post: a rotated part needs its denominators");
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "latent_rope_post: unknown dtype %d", dtype);
+    if (T == 0) return 0;
+    const size_t smem = (size_t)(dr > 0 ? dr : 2) * sizeof(float);
+    cudaError_t e;
+    if (dtype == LI_F32)
+        e = li_launch_pdl(latent_rope_post_kernel<float>, dim3(T), dim3(128), smem, stream, (const float*)low, ld_low, col_c, col_r, (const float*)q, ld_q, d, w,
+                          eps, positions, denom, magnitude, interleaved, (float*)out, nh, R, dr, dl);
+    else
+        e = li_launch_pdl(latent_rope_post_kernel<bf16>, dim3(T), dim3(128), smem, stream, (const bf16*)low, ld_low, col_c, col_r, (const bf16*)q, ld_q, d, w,
+                          eps, positions, denom, magnitude, interleaved, (bf16*)out, nh, R, dr, dl);
+    if (e != cudaSuccess) return li_fail("latent_rope_post: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("latent_rope_post");
+}

@@ -15,6 +15,8 @@
 //     x / (1 + exp(-x)) on the way in.
 //   * li_gla_scan: per head a state S [d, dv] with a decay per token and key channel:  S = diag(a_t) S + k v^T,
 //     o = S^T (q / sqrt(d)),  a_t = sigmoid(z_t)^(1 / tau) from float logits z.
+//   * li_delta_scan: per head a state S [d, dv] under the gated delta rule with a decay per token and key channel:
+//     S = diag(g) S,  u = beta (v - S^T k),  S = S + k u^T,  o = S^T q, with q and k made unit vectors on the way in.
 //   * li_channel_scan: a state S [N] per channel c with a decay per token, channel and element:
 //     S = exp(dt_c A[c, :]) S + dt_c x_c B,  y_c = (S . C + D_c x_c) silu(z_c),  dt = softplus(dt_raw), A = -exp(A_log).
 //   * li_gated_rmsnorm: RMSNorm in equal groups of a float row, with a gate before the norm (y * silu(z)) or after
@@ -453,6 +455,117 @@ gla_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int
             for (int e = 0; e < E; ++e)
                 if (col0 + j < dv && E * lane + e < d) to[(size_t)(col0 + j) * d + E * lane + e] = S[j][e];
     }
+}
+
+// The gated delta rule with a decay per token, head and key channel.  Per head a state S [d, dv]:
+//     S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t      (in this order: o sees the write)
+// A column of S moves on by itself here too (u[c] depends on column c alone), so the walk is the one of gla_scan_kernel:
+// a warp holds eight columns, each lane E neighbouring key channels of all eight.  The two sums over the key channels that
+// a token needs, (gS)^T k and (gS)^T q, are taken together before the write, since S_new^T q = (gS)^T q + u (k . q); k . q
+// is a number per token, taken while staging.  qk [T, stride]: q at column q_off + hk d, k at k_off + hk d with
+// hk = h / (heads / kv_heads), v at v_off + h dv, all after their convolution and activation; q and k are made unit
+// vectors here, x / sqrt(sum x^2 + unit_eps), and q is multiplied by q_scale.  beta = sigmoid(b[T, b_stride] at b_off + h);
+// g = exp(-exp(A_log[h]) softplus(za[T, za_stride] at za_off + h d + i)), za float (the map's bias already added).
+// All of that in float while staging.  One piece per sequence: the rule is not elementwise in S, so chunks of a portion do
+// not run side by side.
+template <typename T, int E>
+__global__ void __launch_bounds__(512)
+delta_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int v_off, const T* __restrict__ b, int b_stride, int b_off,
+                  const float* __restrict__ za, int za_stride, int za_off, const float* __restrict__ A_log, float q_scale, float unit_eps,
+                  float* __restrict__ state, long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
+                  float* __restrict__ out, int heads, int kv_heads, int d, int dv) {
+    constexpr int DP = 32 * E;
+    const int warps = blockDim.x >> 5, cols = kWarpCols * warps;
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;                           // [kStage][DP]
+    float* ks = qs + kStage * DP;               // [kStage][DP]
+    float* as = ks + kStage * DP;               // [kStage][DP] decays
+    float* vs = as + kStage * DP;               // [kStage][cols]
+    float* sc = vs + kStage * cols;             // [kStage][2]: beta, k . q
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y;
+    const int hk = h / (heads / kv_heads);
+    const int q0 = q_start[blockIdx.z], q1 = q_start[blockIdx.z + 1];
+    if (q1 <= q0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col0 = blockIdx.x * cols + warp * kWarpCols;
+    float* st = state + (size_t)slots[blockIdx.z] * state_stride + (size_t)h * dv * d;
+    const float rate = -expf(A_log[h]);
+    float S[kWarpCols][E];
+#pragma unroll
+    for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+        for (int e = 0; e < E; ++e) S[j][e] = (col0 + j < dv && E * lane + e < d) ? st[(size_t)(col0 + j) * d + E * lane + e] : 0.0f;
+    for (int t0 = q0; t0 < q1; t0 += kStage) {
+        const int nt = min(kStage, q1 - t0);
+        __syncthreads();
+        for (int tk = warp; tk < nt; tk += warps) {
+            const T* row = qkv + (size_t)(t0 + tk) * stride;
+            const float* zrow = za + (size_t)(t0 + tk) * za_stride + za_off + h * d;
+            float qq = 0.0f, kk = 0.0f, qk = 0.0f;
+            for (int i = lane; i < DP; i += 32) {
+                const float qv = i < d ? to_float(row[q_off + hk * d + i]) : 0.0f;
+                const float kv = i < d ? to_float(row[k_off + hk * d + i]) : 0.0f;
+                qq = fmaf(qv, qv, qq); kk = fmaf(kv, kv, kk); qk = fmaf(qv, kv, qk);
+                qs[tk * DP + i] = qv;
+                ks[tk * DP + i] = kv;
+                as[tk * DP + i] = i < d ? expf(rate * softplus_f(zrow[i])) : 0.0f;
+            }
+            qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
+            const float fq = q_scale / sqrtf(qq + unit_eps), fk = 1.0f / sqrtf(kk + unit_eps);
+            for (int i = lane; i < DP; i += 32) {                     // (a lane scales what it wrote itself)
+                qs[tk * DP + i] *= fq;
+                ks[tk * DP + i] *= fk;
+            }
+            if (lane == 0) {
+                sc[2 * tk] = sigmoid_f(to_float(b[(size_t)(t0 + tk) * b_stride + b_off + h]));
+                sc[2 * tk + 1] = qk * fq * fk;
+            }
+        }
+        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+            const int tk = e / cols, j = e - tk * cols;
+            const int c = blockIdx.x * cols + j;
+            vs[e] = c < dv ? to_float(qkv[(size_t)(t0 + tk) * stride + v_off + h * dv + c]) : 0.0f;
+        }
+        __syncthreads();
+        for (int tk = 0; tk < nt; ++tk) {
+            float kk[E], aa[E], qq[E], v[kWarpCols], acck[kWarpCols], accq[kWarpCols];
+            load_elements<E>(kk, ks + tk * DP + E * lane);
+            load_elements<E>(aa, as + tk * DP + E * lane);
+            load_elements<E>(qq, qs + tk * DP + E * lane);
+            load_elements<kWarpCols>(v, vs + tk * cols + warp * kWarpCols);
+            const float beta = sc[2 * tk], kq = sc[2 * tk + 1];
+#pragma unroll
+            for (int j = 0; j < kWarpCols; ++j) {
+                acck[j] = accq[j] = 0.0f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    S[j][e] *= aa[e];
+                    acck[j] = fmaf(S[j][e], kk[e], acck[j]);
+                    accq[j] = fmaf(S[j][e], qq[e], accq[j]);
+                }
+            }
+            const float sk = sum8_across_warp(acck, lane), sq = sum8_across_warp(accq, lane);
+            const int jm = column_after_sum8(lane);                   // the column whose sums this lane holds now
+            float vm = v[0];
+#pragma unroll
+            for (int j = 1; j < kWarpCols; ++j) vm = jm == j ? v[j] : vm;
+            const float um = beta * (vm - sk);
+            if ((lane & 3) == 0 && col0 + jm < dv) out[(size_t)(t0 + tk) * heads * dv + h * dv + col0 + jm] = fmaf(um, kq, sq);
+#pragma unroll
+            for (int j = 0; j < kWarpCols; ++j) {
+                const float u = __shfl_sync(0xffffffffu, um, 16 * ((j >> 2) & 1) + 8 * ((j >> 1) & 1) + 4 * (j & 1));
+#pragma unroll
+                for (int e = 0; e < E; ++e) S[j][e] = fmaf(kk[e], u, S[j][e]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+            if (col0 + j < dv && E * lane + e < d) st[(size_t)(col0 + j) * d + E * lane + e] = S[j][e];
 }
 
 // The selective scan with a state row per channel.  x [T, x_stride] at column x_off (after its convolution and activation),
@@ -972,6 +1085,44 @@ LI_EXPORT int li_gla_scan(const void* qkv, int dtype, int stride, int q_off, int
                                                    q_start, slots, out, S, heads, d, dv, seg, mode, chunk_state, chunk_decay, stream)           \
                            : launch_gla<bf16, RR>(qkv, stride, q_off, k_off, v_off, za, za_stride, za_off, inv_tau, q_scale, state, state_stride,   \
                                                   q_start, slots, out, S, heads, d, dv, seg, mode, chunk_state, chunk_decay, stream)
+    if (d <= 32) { LI_SCAN(1); }
+    if (d <= 64) { LI_SCAN(2); }
+    if (d <= 128) { LI_SCAN(4); }
+    LI_SCAN(8);
+#undef LI_SCAN
+}
+
+template <typename T, int E>
+static int launch_delta(const void* qkv, int stride, int q_off, int k_off, int v_off, const void* b, int b_stride, int b_off, const float* za,
+                        int za_stride, int za_off, const float* A_log, float q_scale, float unit_eps, float* state, long long state_stride,
+                        const int* q_start, const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv, cudaStream_t stream) {
+    const int warps = scan_warps(dv), cols = warps * kWarpCols;
+    const size_t smem = ((size_t)3 * kStage * 32 * E + kStage * cols + 2 * kStage) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(delta_scan_kernel<T, E>, dim3(ceil_div(dv, cols), heads, S), dim3(warps * 32), smem, stream, (const T*)qkv, stride,
+                                  q_off, k_off, v_off, (const T*)b, b_stride, b_off, za, za_stride, za_off, A_log, q_scale, unit_eps, state,
+                                  state_stride, q_start, slots, out, heads, kv_heads, d, dv);
+    if (e != cudaSuccess) return li_fail("delta_scan: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("delta_scan");
+}
+
+// The state of a slot: [heads][dv][d] (a column of the head's d x dv matrix at a time).  See delta_scan_kernel.
+LI_EXPORT int li_delta_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const void* b, int b_stride, int b_off,
+                            const float* za, int za_stride, int za_off, const float* A_log, float q_scale, float unit_eps, float* state,
+                            long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv,
+                            cudaStream_t stream) {
+    LI_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && d > 0 && d <= 256 && dv > 0,
+               "delta rule: %d heads on %d key heads of %d x %d (keys of at most 256)", heads, kv_heads, d, dv);
+    LI_REQUIRE(za != nullptr && za_off >= 0 && za_off + heads * d <= za_stride, "delta rule: decays at column %d of %d", za_off, za_stride);
+    LI_REQUIRE(b != nullptr && b_off >= 0 && b_off + heads <= b_stride && A_log != nullptr, "delta rule: write strengths at column %d of %d", b_off, b_stride);
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "delta rule: unknown dtype %d", dtype);
+    if (S == 0) return 0;
+    LI_REQUIRE(S <= 65535 && heads <= 65535, "delta rule: %d sequences or %d heads in one launch", S, heads);
+#define LI_SCAN(RR)                                                                                                                              \
+    return dtype == LI_F32 ? launch_delta<float, RR>(qkv, stride, q_off, k_off, v_off, b, b_stride, b_off, za, za_stride, za_off, A_log, q_scale, \
+                                                     unit_eps, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream)      \
+                           : launch_delta<bf16, RR>(qkv, stride, q_off, k_off, v_off, b, b_stride, b_off, za, za_stride, za_off, A_log, q_scale,  \
+                                                    unit_eps, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream)
     if (d <= 32) { LI_SCAN(1); }
     if (d <= 64) { LI_SCAN(2); }
     if (d <= 128) { LI_SCAN(4); }

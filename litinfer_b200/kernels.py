@@ -522,6 +522,28 @@ def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: f
     _check(library().li_glu_clamped(_p(gate_up), _p(out), _i(_dt(out)), _i(T), _i(I2 // 2), _f(limit), _f(alpha), _stream(out)), "glu_clamped")
 
 
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``out = a N(z) + b N(z^2) + c N(z^3) + e`` per row of ``z`` [T, n], powers element by element, ``N(v) = v / sqrt(mean(v^2)
+    + eps)``; ``coef`` = (a, b, c, e), float32 on the device.  Means and the result in float32, one rounding."""
+    T, n = z.shape
+    _need(z, "polynorm input")
+    _need(coef, "polynorm coefficients", torch.float32, (4,))
+    _need(out, "polynorm output", z.dtype, (T, n))
+    _check(library().li_polynorm(_p(z), _i(_dt(z)), _p(coef), _f(eps), _p(out), _i(T), _i(n), _stream(out)), "polynorm")
+
+
+def mul_sigmoid(x: torch.Tensor, gate: torch.Tensor, gate_col: int = 0, group: int = 1) -> None:
+    """``x[t, i] *= sigmoid(gate[t, gate_col + i // group])`` in place (float32 arithmetic, one rounding): an output gate per
+    element, or with ``group`` a head's width one per head."""
+    T, n = x.shape
+    _need(x, "gated activation")
+    _need(gate, "gate", x.dtype)
+    if gate.dim() != 2 or gate.shape[0] != T or group < 1 or n % group or gate_col + n // group > gate.shape[1]:
+        raise KernelError(f"mul_sigmoid: a gate of shape {tuple(gate.shape)} from column {gate_col} for {T} rows of {n} in groups of {group}")
+    _check(library().li_mul_sigmoid(_p(x), _p(gate), _i(_dt(x)), _i(gate.shape[1]), _i(int(gate_col)), _i(int(group)), _i(T), _i(n), _stream(x)),
+           "mul_sigmoid")
+
+
 class WeightedPair:
     """Two activations that stand for ``sa * a + sb * b`` (two mixers side by side) until a kernel that consumes the sum
     takes it in (:func:`hc_update`); :meth:`materialize` adds them up with a kernel of its own."""
@@ -783,6 +805,32 @@ def gla_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, za: torch.Te
     run(chunks.seg, chunks.count, 2, cstate, cdecay)
 
 
+def delta_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, b: torch.Tensor, b_col: int, za: torch.Tensor, za_col: int,
+               A_log: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, out32: torch.Tensor, heads: int,
+               kv_heads: int, dim: int, vdim: int, unit_eps: float = 1e-6) -> None:
+    """The gated delta rule with a decay per token, head and key channel, state ``S [dim, vdim]`` per head at the start of
+    ``state[slot]`` (kept column by column, ``[heads, vdim, dim]``): ``S = diag(g_t) S``; ``u = beta_t (v_t - S^T k_t)``;
+    ``S = S + k_t u^T``; ``out_t = S^T q_t``.  q and k (``kv_heads`` heads of ``dim``; head h uses ``h // (heads / kv_heads)``) are
+    the columns of ``qkv`` at ``q_col`` and ``k_col``, made unit vectors here (``x / sqrt(sum x^2 + unit_eps)``, q also times
+    ``dim^-1/2``); v (``heads`` of ``vdim``) at ``v_col``; ``beta = sigmoid(b[:, b_col + h])``;
+    ``g = exp(-exp(A_log[h]) softplus(za[:, za_col + h dim + i]))`` with ``za`` float32.  A sequence's tokens run in order,
+    in one piece."""
+    T = qkv.shape[0]
+    _need(qkv, "q|k|v")
+    _need(b, "write strengths", qkv.dtype)
+    _need(za, "decay inputs", torch.float32)
+    _need(A_log, "A_log", torch.float32, (heads,))
+    _need(out32, "scan output", torch.float32, (T, heads * vdim))
+    S = q_start.shape[0] - 1
+    _need(slots, "state slots", torch.int32, (S,))
+    st, stride, _ = _state_args(state, 0)
+    if heads * dim * vdim > state.shape[1] or za.shape[0] != T or b.shape[0] != T:
+        raise KernelError("delta_scan: the state, the decays or the write strengths are too small")
+    _check(library().li_delta_scan(_p(qkv), _i(_dt(qkv)), _i(qkv.shape[1]), _i(q_col), _i(k_col), _i(v_col), _p(b), _i(b.shape[1]), _i(b_col),
+                                   _p(za), _i(za.shape[1]), _i(za_col), _p(A_log), _f(float(dim) ** -0.5), _f(float(unit_eps)), st, stride,
+                                   _p(q_start), _p(slots), _p(out32), _i(S), _i(heads), _i(kv_heads), _i(dim), _i(vdim), _stream(out32)), "delta_scan")
+
+
 def channel_scan(x: torch.Tensor, x_col: int, bc: torch.Tensor, b_col: int, c_col: int, dt32: torch.Tensor, z: torch.Tensor, z_col: int,
                  A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, y: torch.Tensor,
                  chunks: Optional[ScanChunks] = None) -> None:
@@ -856,11 +904,15 @@ class RowSum:
         return y
 
 
+SCALE_ONLY = 2          # the `centered` of a "norm" that is a factor per channel and nothing else
+
+
 def norm_add_norm(x32: torch.Tensor, y, post: Optional[tuple], nxt: Optional[tuple], out: Optional[torch.Tensor],
                   rows: Optional[torch.Tensor] = None) -> None:
     """Per token: ``x32 += post(y)``, then ``out = nxt(x32)``.  A norm is a tuple ``(weight, centered, eps)``: centered takes
     the mean off and divides by the root of the variance (mean of squared deviations) + eps, not centered divides by the
-    root of the mean of squares + eps; both multiply by the weight.  ``post`` None: ``x32 += y``; ``y`` None: nothing is
+    root of the mean of squares + eps; both multiply by the weight.  ``centered`` 2 (:data:`SCALE_ONLY`): no statistic at
+    all, the row times the weight (a learned factor per channel).  ``post`` None: ``x32 += y``; ``y`` None: nothing is
     added; ``nxt`` None: no output; ``nxt`` with a weight of None: ``out`` is ``x32`` as it is, in the run dtype.  ``rows`` (int32, only without ``y``): ``out[r] = nxt(x32[rows[r]])``.  ``y`` may be a
     :class:`RowSum`: the sum is then taken inside this kernel, in float32."""
     n_src, H = x32.shape
@@ -892,7 +944,7 @@ def norm_add_norm(x32: torch.Tensor, y, post: Optional[tuple], nxt: Optional[tup
     if nxt is not None:
         _need(out, "normalised output", y.dtype if y is not None else None, (R, H))
     dt = _dt(y) if y is not None else _dt(out)
-    _check(library().li_norm_add_norm(_p(x32), _p(y), _i(dt), _p(wp), _i(1 if cp else 0), _f(ep), _p(wn), _i(1 if cn else 0), _f(en),
+    _check(library().li_norm_add_norm(_p(x32), _p(y), _i(dt), _p(wp), _i(int(cp)), _f(ep), _p(wn), _i(int(cn)), _f(en),
                                       _p(out if nxt is not None else None), _p(rows), _i(R), _i(n_src), _i(H), _p(places), _i(top), _p(y_weights),
                                       _stream(x32)), "norm_add_norm")
 
@@ -978,6 +1030,31 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
         _i(1 if write else 0), _i(1 if shift else 0), _i(1 if to_cache else 0), _i(out.shape[1]), _stream(out)), "conv_norm_rope_kv")
 
 
+def latent_rope_post(low: torch.Tensor, col_c: int, col_r: int, q: torch.Tensor, dim: int, weight: torch.Tensor, eps: float,
+                     positions: torch.Tensor, denominators: Optional[torch.Tensor], magnitude: float, interleaved: bool, out: torch.Tensor,
+                     num_heads: int, rank: int, rot_dim: int, head: int) -> None:
+    """Latent attention with a rotated part, per token: ``c = rmsnorm(low[:, col_c : col_c + rank]) * weight`` into the first
+    ``rank`` columns of the key head and of the value head of ``out`` [T, (num_heads + 2) head]; the one rotated key part all
+    heads share, ``low[:, col_r : col_r + rot_dim]``, rotated, behind c in the key head; every query head's rotated part
+    (the last ``rot_dim`` of its ``dim + rot_dim`` columns of ``q``) rotated, behind the head's first ``rank`` columns of
+    ``out`` (which are not touched); the rest of every head zeros.  Pair i turns by ``position / denominators[i]``;
+    ``interleaved``: the pair is (2i, 2i + 1), else (i, i + rot_dim / 2); cosines and sines are multiplied by ``magnitude``."""
+    T = low.shape[0]
+    _need(low, "latent projection")
+    _need(q, "queries", low.dtype)
+    _need(weight, "latent norm weight", torch.float32, (rank,))
+    _need(positions, "positions", torch.int32, (T,))
+    if rot_dim:
+        _need(denominators, "rope denominators", torch.float32, (rot_dim // 2,))
+    _need(out, "attention rows", low.dtype, (T, (num_heads + 2) * head))
+    if q.shape[0] != T:
+        raise KernelError(f"latent_rope_post: {q.shape[0]} query rows for {T} tokens")
+    _check(library().li_latent_rope_post(_p(low), _i(_dt(low)), _i(low.shape[1]), _i(int(col_c)), _i(int(col_r)), _p(q), _i(q.shape[1]), _i(int(dim)),
+                                         _p(weight), _f(eps), _p(positions), _p(denominators if rot_dim else None), _f(float(magnitude)),
+                                         _i(1 if interleaved else 0), _p(out), _i(T), _i(num_heads), _i(rank), _i(rot_dim), _i(head), _stream(out)),
+           "latent_rope_post")
+
+
 def row_rinv(x: torch.Tensor, ranges, eps: float, out: torch.Tensor) -> None:
     """``out[t, j] = 1 / sqrt(sum(x[t, col_j : col_j + n_j]^2) / width_j + eps)`` for one or two ``ranges`` (col, n, width):
     the factor of an RMS norm over a whole projection (``width``: how many of the n columns are real, the rest zero padding)."""
@@ -998,20 +1075,26 @@ def row_rinv(x: torch.Tensor, ranges, eps: float, out: torch.Tensor) -> None:
 
 def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_offsets: Optional[torch.Tensor] = None,
                    a_group_cols: int = 0, out_group_cols: int = 0, tile_group: Optional[torch.Tensor] = None,
-                   epilogue: Optional[str] = None) -> None:
+                   epilogue: Optional[str] = None, epilogue_params: Optional[torch.Tensor] = None) -> None:
     """``weight`` [G, N, K]: a product per group.  With ``row_offsets`` (int32 [G + 1] on the device) group g owns the rows
     ``row_offsets[g] .. row_offsets[g + 1] - 1`` of ``a`` [M, K] and ``out`` [M, N].  Without, every group takes all rows, its
     inputs at column ``g * a_group_cols`` of ``a`` and its outputs at column ``g * out_group_cols`` of ``out`` (a map per head).
     ``tile_group`` (int32 on the device; from :func:`moe_sort` with ``pad`` 128): the group of every tile of 128 rows when
     the groups' runs start at multiples of 128; large bfloat16 products then run on the tcgen05 tiles.
     ``epilogue="swiglu"`` (bfloat16, rows in groups): every group's matrix holds gate and up rows interleaved in eights
-    (:func:`interleave_gate_up` per group) and ``out`` [M, N / 2] takes ``up * gate / (1 + exp(-gate))``."""
+    (:func:`interleave_gate_up` per group) and ``out`` [M, N / 2] takes ``up * gate / (1 + exp(-gate))``.
+    ``epilogue="glu_clamped"``: the same layout, the gated unit with bounded operands; ``epilogue_params`` holds its (limit,
+    alpha), float32 on the device.  Rows that belong to no group (behind ``row_offsets[G]``) are left as they are."""
     G, N, Kd = weight.shape
-    if epilogue not in (None, "swiglu"):
+    if epilogue not in (None,) + GATED:
         raise KernelError(f"grouped_linear: unknown epilogue {epilogue!r}")
-    if epilogue == "swiglu":
+    if (epilogue == "glu_clamped") != (epilogue_params is not None):
+        raise KernelError("grouped_linear: the bounded unit needs its parameters, the other epilogues take none")
+    if epilogue_params is not None:
+        _need(epilogue_params, "parameters of the gated unit", torch.float32, (2,))
+    if epilogue in GATED:
         if a.dtype != torch.bfloat16 or row_offsets is None or N % 16 or Kd % 8:
-            raise KernelError("grouped_linear: the swiglu epilogue takes bfloat16 rows in groups, K a multiple of 8, N a multiple of 16")
+            raise KernelError("grouped_linear: a gated epilogue takes bfloat16 rows in groups, K a multiple of 8, N a multiple of 16")
         N_out = N // 2
     else:
         N_out = N
@@ -1032,7 +1115,8 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row
         if row_offsets is None or tile_group.numel() * 128 < M:
             raise KernelError("grouped_linear: a table of the tiles' groups goes with row offsets and covers every tile of 128 rows")
     _check(library().li_grouped_linear(_p(a), _i(a.shape[1]), _i(a_group_cols), _p(weight), _p(out), _i(out.shape[1]), _i(out_group_cols),
-                                       _p(row_offsets), _p(tile_group), _i(_dt(a)), _i(M), _i(N), _i(Kd), _i(G), _i(EPILOGUES[epilogue]), _stream(out)),
+                                       _p(row_offsets), _p(tile_group), _i(_dt(a)), _i(M), _i(N), _i(Kd), _i(G), _i(EPILOGUES[epilogue]), _p(epilogue_params),
+                                       _stream(out)),
            "grouped_linear")
 
 
@@ -1050,17 +1134,34 @@ def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.
            "moe_route")
 
 
+def moe_route_grouped(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int, scale: float,
+                      ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Routing over all experts at once: ``s = softmax(logits)``; the choice scores are ``s + correction``; the experts form
+    ``groups`` equal groups of neighbours, a group's score is its largest choice score, and only experts of the ``keep`` best
+    groups can be chosen; the ``top`` largest choice scores choose (the lower index wins a tie); ``weights`` are the chosen
+    experts' s divided by their sum (+ 1e-20), times ``scale``."""
+    T, E = logits.shape
+    _need(logits, "router logits", torch.float32)
+    if correction is not None:
+        _need(correction, "correction of the choice scores", torch.float32, (E,))
+    _need(ids, "expert ids", torch.int32, (T, top))
+    _need(weights, "expert weights", torch.float32, (T, top))
+    _check(library().li_moe_route_grouped(_p(logits), _p(correction), _i(T), _i(E), _i(top), _i(int(groups)), _i(int(keep)), _f(float(scale)),
+                                          _p(ids), _p(weights), _stream(ids)), "moe_route_grouped")
+
+
 def sorted_rows(pairs: int, experts: int, pad: int = 1) -> int:
     """How many places the sorted order of ``pairs`` (token, choice) pairs has when every expert's run starts at a multiple of ``pad``."""
     return pairs if pad <= 1 else -(-(pairs + experts * (pad - 1)) // pad) * pad
 
 
 def moe_sort(ids: torch.Tensor, experts: int, offsets: torch.Tensor, pair_at: torch.Tensor, place_of: torch.Tensor, pad: int = 1,
-             tile_group: Optional[torch.Tensor] = None) -> None:
+             tile_group: Optional[torch.Tensor] = None, matrices: Optional[int] = None) -> None:
     """A stable sort of the (token, choice) pairs by expert: ``offsets`` [experts + 1] (where each expert's rows start),
     ``pair_at`` (which pair stands at a sorted place; -1: none), ``place_of`` [n] (the sorted place of a pair).  ``pad`` > 1:
     every expert's run starts at a multiple of it, ``pair_at`` has :func:`sorted_rows` places, and ``tile_group`` (if given, one
-    entry per ``pad`` places) says which expert each tile of ``pad`` rows belongs to (-1 behind the last run)."""
+    entry per ``pad`` places) says which expert each tile of ``pad`` rows belongs to (-1 behind the last run, and for the
+    experts from ``matrices`` on: experts without matrices, whose rows a grouped product leaves as they are)."""
     n = ids.numel()
     R = sorted_rows(n, experts, pad)
     _need(ids, "expert ids", torch.int32)
@@ -1071,7 +1172,7 @@ def moe_sort(ids: torch.Tensor, experts: int, offsets: torch.Tensor, pair_at: to
     if tile_group is not None:
         tiles = R // pad
         _need(tile_group, "groups of the row tiles", torch.int32, (tiles,))
-    _check(library().li_moe_sort(_p(ids), _i(n), _i(experts), _i(int(pad)), _p(offsets), _p(pair_at), _p(place_of), _p(tile_group), _i(tiles),
+    _check(library().li_moe_sort(_p(ids), _i(n), _i(experts), _i(experts if matrices is None else int(matrices)), _i(int(pad)), _p(offsets), _p(pair_at), _p(place_of), _p(tile_group), _i(tiles),
                                  _i(R), _stream(ids)), "moe_sort")
 
 

@@ -99,6 +99,8 @@ class PagedAttention(Mixer):
         self.gate = FusedLinear(prefix, [gate], self.hidden, [self.num_heads], False, dtype, suffixes=suffixes) if gate else None
         position = spec.get("position")
         self.position = POSITIONS.build(position, prefix, dtype, device, head_dim=self.head_dim) if position is not None else None
+        if getattr(self.position, "interleaved", False) or getattr(self.position, "magnitude", 1.0) != 1.0:
+            raise ValueError(f"attention at {prefix!r}: its kernels rotate halves of a head with plain cosines and sines")
         self.conv_names = [prefix + n + str(spec.get("conv_suffix", ".conv")) for n in stems] if self.taps >= 1 else []
         self.norm_names = [prefix + str(qk_norm[n]) for n in (("q",) if self.shared_kv else ("q", "k"))] if qk_norm else []
         self.conv_weight = self.q_norm = self.k_norm = None

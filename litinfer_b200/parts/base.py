@@ -246,11 +246,15 @@ class Norm(Part):
 class Rotary:
     """What a mixer's kernels need to rotate queries and keys of this step: pair ``j`` of the first ``rotary_dim``
     elements of a head turns by ``position / denominators[j]``; ``table`` (or None) holds the cosines and sines
-    of the step's tokens, ``[tokens, rotary_dim / 2, 2]`` float32, for kernels that rotate in an epilogue."""
+    of the step's tokens, ``[tokens, rotary_dim / 2, 2]`` float32, for kernels that rotate in an epilogue.  ``magnitude``: a
+    factor on cosines and sines; ``interleaved``: pair j is elements 2j and 2j + 1 instead of j and j + rotary_dim / 2.  A
+    mixer whose kernels know neither refuses a position part that asks for them."""
 
     denominators: torch.Tensor
     rotary_dim: int
     table: Optional[torch.Tensor] = None
+    magnitude: float = 1.0
+    interleaved: bool = False
 
 
 class Position(Part):

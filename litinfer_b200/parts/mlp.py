@@ -75,3 +75,37 @@ class ClampedGLU(FeedForward):
 
     def forward(self, h, ctx):
         return self.down(self.gate_up.activation(h))
+
+
+@FEED_FORWARDS.register("polynorm_mlp")
+class PolyNormMLP(FeedForward):
+    """A dense feed-forward with one inner product and the PolyNorm activation: ``down(act(up(h)))``, both products with
+    biases, ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e`` with powers element by element, ``N(v) = v / sqrt(mean(v^2) + eps)``
+    over the token's inner vector, and (a, b, c, e) a stored tensor of four numbers.  The three means and the sum are
+    float32; the result is rounded once."""
+
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.hidden = int(spec["hidden_size"])
+        self.intermediate = int(spec["intermediate_size"])
+        self.eps = float(spec["eps"])
+        names = spec.get("names", {})
+        suffixes = tuple(spec.get("suffixes", (".weight", ".bias")))
+        self.up = FusedLinear(prefix, [names.get("up", "up_proj")], self.hidden, [self.intermediate], True, dtype, suffixes=suffixes)
+        self.down = FusedLinear(prefix, [names.get("down", "down_proj")], self.intermediate, [self.hidden], True, dtype, suffixes=suffixes)
+        self.act_name = prefix + names.get("act", "act")
+        self.coef = None
+
+    def params(self) -> List[ParamSpec]:
+        return self.up.params() + self.down.params() + [ParamSpec(self.act_name, (4,), role="vector", mean=0.3, std=0.2)]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.up.bind(tensors)
+        self.down.bind(tensors)
+        self.coef = tensors.pop(self.act_name).contiguous()
+
+    def forward(self, h, ctx):
+        z = self.up(h)
+        act = torch.empty_like(z)
+        K.polynorm(z, self.coef, self.eps, act)
+        return self.down(act)

@@ -2,8 +2,11 @@
 (src/ops/rms_norm/op.cpp:13-24).  Sum, reciprocal root and products in
 float32 on the float32 residual stream; one rounding of y to the run dtype.
 ``gain`` (a parameter of the spec, default 1) is a constant factor on the result, multiplied into the
-weight once when it is bound: a block that adds ``gain * norm(y)`` to the stream.  Kind ``identity``
-is no norm at all: the stream as it is, in the run dtype, for a sublayer that reads the stream itself."""
+weight once when it is bound: a block that adds ``gain * norm(y)`` to the stream.  ``offset`` (default 0) is added to
+the stored weight when it is bound: a weight that is stored around zero and applied as ``offset + w``.  Kind ``identity``
+is no norm at all: the stream as it is, in the run dtype, for a sublayer that reads the stream itself.  Kind
+``channel_scale`` is no norm either: a learned factor per channel (stored as it is applied), for an arrangement that
+multiplies a sublayer's output by one before it joins the stream."""
 
 from __future__ import annotations
 
@@ -36,13 +39,19 @@ class RMSNorm(Norm):
         self.eps = float(spec["eps"])
         self.tensor = self.prefix + str(spec.get("tensor", "weight"))      # the weight's name below the prefix
         self.gain = float(spec.get("gain", 1.0))
+        self.offset = float(spec.get("offset", 0.0))
         self.weight = None
 
     def params(self) -> List[ParamSpec]:
+        # (a weight that is applied as offset + w is stored around 1 - offset)
+        if self.offset:
+            return [ParamSpec(self.tensor, (self.size,), role="vector", mean=1.0 - self.offset, std=0.1)]
         return [ParamSpec(self.tensor, (self.size,), role="vector", init="ones_normal")]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors.pop(self.tensor)
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
         if self.gain != 1.0:
             self.weight = (self.weight * self.gain).contiguous()
 
@@ -141,6 +150,44 @@ class NoNorm(Norm):
 
     def statistics(self):
         return (None, False, 0.0)
+
+    def forward(self, x32):
+        out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+        K.norm_add_norm(x32, None, None, self.statistics(), out)
+        return out
+
+    def add_forward(self, x32, delta):
+        out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+        K.norm_add_norm(x32, delta, None, self.statistics(), out)
+        return out
+
+    def gather_forward(self, x32, rows):
+        out = torch.empty((rows.shape[0], x32.shape[1]), dtype=self.dtype, device=x32.device)
+        K.norm_add_norm(x32, None, None, self.statistics(), out, rows=rows)
+        return out
+
+
+@NORMS.register("channel_scale")
+class ChannelScale(Norm):
+    """A learned factor per channel and nothing else: ``y = x * w``.  It stands where an arrangement expects the norm behind
+    a sublayer (``sandwich``: ``x += post(sublayer(pre(x)))``) and the design multiplies the sublayer's output by a vector
+    before it joins the stream.  ``statistics()`` says so with the mode :data:`litinfer_b200.kernels.SCALE_ONLY`, which the
+    pass over the stream takes as "the row times the weight"."""
+
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.size = int(spec["size"])
+        self.tensor = self.prefix + str(spec.get("tensor", "weight"))
+        self.weight = None
+
+    def params(self) -> List[ParamSpec]:
+        return [ParamSpec(self.tensor, (self.size,), role="vector", mean=float(self.spec.get("mean", 1.0)), std=float(self.spec.get("std", 0.1)))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors.pop(self.tensor)
+
+    def statistics(self):
+        return (self.weight, K.SCALE_ONLY, 0.0)
 
     def forward(self, x32):
         out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)

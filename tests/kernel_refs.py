@@ -232,6 +232,8 @@ def _norm_of(v, spec):
     v = v.float()
     if weight is None:                                    # no norm: the row as it is
         return v
+    if int(centered) == 2:                                # a factor per channel and no statistic
+        return v * weight
     if centered:
         v = v - v.mean(-1, keepdim=True)
     return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight
@@ -342,7 +344,7 @@ def add_pair_rows(x32, pairs, ids, positions, q_start, seq_of_token, slots, stat
         state[sl[s], 0] = prev
 
 
-def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_cols=0, tile_group=None, epilogue=None):
+def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_cols=0, tile_group=None, epilogue=None, epilogue_params=None):
     G, N, Kd = weight.shape
     if row_offsets is not None:
         offs = row_offsets.tolist()
@@ -354,6 +356,11 @@ def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_c
                     y = y.view(hi - lo, N // 16, 2, 8)                 # columns come as 8 gate, 8 up, 8 gate, 8 up, ...
                     gate, up = y[:, :, 0, :], y[:, :, 1, :]
                     y = (up * (gate / (1.0 + torch.exp(-gate)))).reshape(hi - lo, N // 2)
+                elif epilogue == "glu_clamped":
+                    limit, alpha = (float(x) for x in epilogue_params.tolist())
+                    y = y.view(hi - lo, N // 16, 2, 8)
+                    gate, up = torch.clamp(y[:, :, 0, :], max=limit), torch.clamp(y[:, :, 1, :], min=-limit, max=limit)
+                    y = (gate / (1.0 + torch.exp(-alpha * gate)) * (up + 1.0)).reshape(hi - lo, N // 2)
                 out[lo:hi] = y.to(out.dtype)
         return
     for g in range(G):
@@ -378,7 +385,7 @@ def sorted_rows(pairs, experts, pad=1):
     return pairs if pad <= 1 else -(-(pairs + experts * (pad - 1)) // pad) * pad
 
 
-def moe_sort(ids, experts, offsets, pair_at, place_of, pad=1, tile_group=None):
+def moe_sort(ids, experts, offsets, pair_at, place_of, pad=1, tile_group=None, matrices=None):
     flat = ids.reshape(-1).long()
     counts = torch.bincount(flat, minlength=experts).tolist()
     pair_at.fill_(-1)
@@ -392,7 +399,7 @@ def moe_sort(ids, experts, offsets, pair_at, place_of, pad=1, tile_group=None):
         place_of[mine] = torch.arange(start, start + counts[e], dtype=torch.int32, device=ids.device)
         run = -(-counts[e] // pad) * pad
         if tile_group is not None:
-            tile_group[start // pad:(start + run) // pad] = e
+            tile_group[start // pad:(start + run) // pad] = e if matrices is None or e < matrices else -1
         start += run
     offsets[experts] = start
 
@@ -578,6 +585,85 @@ def gated_rmsnorm(y32, gate, gate_col, weight, eps, groups, gate_first, out, gat
     _store(out, v if gate_first else v * (_silu(z) if gate_act == "silu" else torch.sigmoid(z)))
 
 
+
+def moe_route_grouped(logits, correction, top, groups, keep, scale, ids, weights):
+    s = torch.softmax(logits.float(), dim=-1)
+    T, E = s.shape
+    choice = s + correction if correction is not None else s.clone()
+    if keep < groups:
+        best = choice.view(T, groups, E // groups).max(dim=-1).values
+        order = torch.sort(best, dim=-1, descending=True, stable=True).indices[:, :keep]
+        kept = torch.zeros((T, groups), dtype=torch.bool, device=s.device)
+        kept.scatter_(1, order, True)
+        choice = choice.masked_fill(~kept[:, :, None].expand(T, groups, E // groups).reshape(T, E), float("-inf"))
+    chosen = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :top]
+    sc = torch.gather(s, 1, chosen)
+    ids.copy_(chosen.to(torch.int32))
+    weights.copy_(sc / (sc.sum(-1, keepdim=True) + 1e-20) * scale)
+
+
+def polynorm(z, coef, eps, out):
+    a, b, c, e = (float(x) for x in coef.tolist())
+    v = z.float()
+
+    def n(u):
+        return u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps)
+
+    _store(out, a * n(v) + b * n(v * v) + c * n(v * v * v) + e)
+
+
+def mul_sigmoid(x, gate, gate_col=0, group=1):
+    T, n = x.shape
+    g = gate[:, gate_col:gate_col + n // group].float().repeat_interleave(group, dim=1)
+    _store(x, x.float() * torch.sigmoid(g))
+
+
+def latent_rope_post(low, col_c, col_r, q, dim, weight, eps, positions, denominators, magnitude, interleaved, out, num_heads, rank, rot_dim, head):
+    T = low.shape[0]
+    c = low[:, col_c:col_c + rank].float()
+    c = (c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * weight).to(out.dtype)
+    rows = out.view(T, num_heads + 2, head)
+    rows[:, num_heads, :rank] = c
+    rows[:, num_heads + 1, :rank] = c
+    rows[:, num_heads + 1, rank:] = 0
+    rows[:, :num_heads + 1, rank + rot_dim:] = 0
+    if not rot_dim:
+        return
+    half = rot_dim // 2
+    ang = positions.float()[:, None] / denominators[None, :]
+    cs, sn = (torch.cos(ang) * magnitude)[:, None, :], (torch.sin(ang) * magnitude)[:, None, :]
+    src = torch.cat([q[:, :num_heads * (dim + rot_dim)].reshape(T, num_heads, dim + rot_dim)[:, :, dim:], low[:, None, col_r:col_r + rot_dim]], dim=1).float()
+    ia = torch.arange(0, rot_dim, 2) if interleaved else torch.arange(0, half)
+    ib = ia + 1 if interleaved else ia + half
+    a, b = src[..., ia], src[..., ib]
+    res = torch.empty_like(src)
+    res[..., ia] = a * cs - b * sn
+    res[..., ib] = b * cs + a * sn
+    rows[:, :num_heads + 1, rank:rank + rot_dim] = res.to(out.dtype)
+
+
+def delta_scan(qkv, q_col, k_col, v_col, b, b_col, za, za_col, A_log, state, q_start, slots, out32, heads, kv_heads, dim, vdim, unit_eps=1e-6):
+    starts, sl = q_start.tolist(), slots.tolist()
+    rep = heads // kv_heads
+    for s in range(len(starts) - 1):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo:
+            continue
+        S = state[sl[s], :heads * dim * vdim].view(heads, vdim, dim).transpose(1, 2)      # kept column by column: [heads][vdim][dim]
+        for t in range(lo, hi):
+            row = qkv[t].float()
+            q = row[q_col:q_col + kv_heads * dim].view(kv_heads, dim)
+            k = row[k_col:k_col + kv_heads * dim].view(kv_heads, dim)
+            q = (q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * float(dim) ** -0.5).repeat_interleave(rep, dim=0)
+            k = (k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(rep, dim=0)
+            v = row[v_col:v_col + heads * vdim].view(heads, vdim)
+            beta = torch.sigmoid(b[t, b_col:b_col + heads].float())
+            g = torch.exp(-torch.exp(A_log)[:, None] * torch.nn.functional.softplus(za[t, za_col:za_col + heads * dim].float(), threshold=1e9).view(heads, dim))
+            S.mul_(g[:, :, None])
+            u = beta[:, None] * (v - torch.einsum("hdv,hd->hv", S, k))
+            S.add_(k[:, :, None] * u[:, None, :])
+            out32[t] = torch.einsum("hdv,hd->hv", S, q).reshape(heads * vdim)
+
 def argmax(logits, out):
     # first maximum
     m = logits.max(dim=1, keepdim=True).values
@@ -667,7 +753,7 @@ def table_gather(resident, updates, slots, out, trash_page):
             out[s, b] = resident[slot, b] if b < cols else trash_page
 
 
-ALL = ["row_rinv", "add_pair_rows", "gla_scan", "channel_scan", "sorted_rows", "norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route", "moe_sort", "moe_gather", "moe_combine",
+ALL = ["moe_route_grouped", "polynorm", "mul_sigmoid", "latent_rope_post", "delta_scan", "row_rinv", "add_pair_rows", "gla_scan", "channel_scan", "sorted_rows", "norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route", "moe_sort", "moe_gather", "moe_combine",
        "glu_clamped", "weighted_sum2", "add_position_rows", "hc_expand", "hc_read_norm", "hc_update", "causal_conv_silu", "conv_state_shift", "ssm_scan",
        "decay_scan", "gated_rmsnorm", "table_gather", "gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]
