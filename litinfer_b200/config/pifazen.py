@@ -176,7 +176,9 @@ class PifazenConfig:
             raise ConfigError(f"config.json: {where}mlp needs 'router' (experts, top, ...) and 'expert' (ff, limit)")
         rw = where + "mlp.router."
         experts, top = _int(router, "experts", rw), _int(router, "top", rw)
-        identity = _opt_int(router, "identity", rw) or 0
+        identity = router.get("identity") or 0                 # none, or a count that may be zero
+        if isinstance(identity, bool) or not isinstance(identity, int) or identity < 0:
+            raise ConfigError(f"config.json: {rw}'identity' must be a count of identity experts, got {identity!r}")
         groups = router.get("groups")
         count = keep = 1
         if groups is not None:
