@@ -25,8 +25,8 @@ Weights (3 GB) are larger than L2, so nothing stays cached between steps.
 profiling runs and the summaries under ``profiles/``); ``mixed`` is a step of ``--batch`` requests decoding at
 ``--context`` beside a portion of ``--prefill-tokens`` prompt tokens.
 
-``--only design`` runs a design (``--design filasun|gorulorn|demavik``, default filasun) beside the Qwen2 model of equal layer sizes and layer count (``--design-shapes``,
-``--layers``, default 6): prefill of ``--prefill-tokens`` tokens and decode at batch 1, 8 and 32; ``--arch filasun|gorulorn|demavik`` puts
+``--only design`` runs a design (``--design filasun|gorulorn|demavik|pifazen``, default filasun) beside the Qwen2 model of equal layer sizes and layer count (``--design-shapes``,
+``--layers``, default 6): prefill of ``--prefill-tokens`` tokens and decode at batch 1, 8 and 32; ``--arch filasun|gorulorn|demavik|pifazen`` puts
 that design behind ``--only decode|prefill|kernels-decode|kernels-prefill`` (the kernel tables of ``profiles/``).
 
 ``--shape 1.5b|7b|14b`` chooses the layer sizes (default 1.5b, the headline; the other two are the larger workloads of
@@ -156,13 +156,42 @@ def demavik_config(shape: str, layers: int):
             "max_positions": d["max_position_embeddings"]}
 
 
+def pifazen_config(shape: str, layers: int):
+    """A Pifazen model with the layer sizes of a shape of the benchmark description: the same width, head count (at most 16
+    on the one latent head), value size and vocabulary as the Qwen2 model of that shape.  Layers go round three kinds:
+    latent attention with queries through a latent of half the width (64 unrotated and 32 rotated elements a head, a
+    key/value latent of 96: the attention over the latent has heads of 128), the gated delta rule (keys and values of
+    head size, 4 taps, ranks of 16 and 32), and latent attention with queries straight from the input and blended
+    frequencies.  The first layer has the dense feed-forward of the shape's width, the others 8 experts of half that
+    width and 2 identity experts, 2 choices per token out of 3 of 5 groups; the last layer runs on the tensors of the
+    layer three before it."""
+    d = SHAPES[shape]
+    H, nh, dh = d["hidden_size"], d["num_attention_heads"], d["head_dim"]
+    moe = {"kind": "moe", "expert": {"ff": d["intermediate_size"] // 2, "limit": 7.0},
+           "router": {"experts": 8, "identity": 2, "top": 2, "scale": 1.5, "groups": {"count": 5, "keep": 3}}}
+    rot = {"dims": 32, "base": d["rope_theta"]}
+    la = {"heads": min(nh, 16), "dim": 64, "rot_dim": 32, "vdim": dh, "kv_rank": 96, "q_rank": H // 2, "rot": rot, "scale": 96 ** -0.5}
+    la2 = {"heads": min(nh, 16), "dim": 64, "rot_dim": 32, "vdim": dh, "kv_rank": 96, "scale": 96 ** -0.5,
+           "rot": dict(rot, scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})}
+    dl = {"heads": nh, "kv_heads": nh, "dim": dh, "vdim": dh, "conv": 4, "decay_rank": 16, "gate_rank": 32}
+    out = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": d["intermediate_size"]} if i == 0 else moe
+        kind = i % 3
+        out.append({"type": ("latent_attention", "channel_delta", "latent_attention_2")[kind], "mlp": mlp, "mixer": dict((la, dl, la2)[kind])})
+    if layers >= 5:
+        out[-1] = dict(out[layers - 4], weights_of=layers - 4)
+    return {"architecture": "Pifazen", "layers": out, "norm": {"eps": 1e-6}, "vocab": d["vocab_size"], "width": H,
+            "max_positions": d["max_position_embeddings"]}
+
+
 def design_layer_runs(cfg) -> int:
     loop = cfg.get("loop")
     return len(cfg["layers"]) + ((loop["stop"] - loop["start"]) * (loop["times"] - 1) if loop else 0)
 
 
 def time_design(args, peaks):
-    """Prefill and decode of a design (``--design filasun|gorulorn|demavik``) beside the Qwen2 model of the same layer sizes and as
+    """Prefill and decode of a design (``--design filasun|gorulorn|demavik|pifazen``) beside the Qwen2 model of the same layer sizes and as
     many layers as the design runs (random weights), through the same step function: tokens per second, and the
     milliseconds behind them."""
     import torch
@@ -183,6 +212,8 @@ def time_design(args, peaks):
                 runs = design_layer_runs(cfg)
             elif arch == "demavik":
                 cfg = demavik_config(shape, layers)
+            elif arch == "pifazen":
+                cfg = pifazen_config(shape, layers)
             else:
                 cfg = bench_config(shape)
                 cfg["num_hidden_layers"] = runs
@@ -780,8 +811,8 @@ def main() -> int:
     ap.add_argument("--kernel-rows", type=int, default=16, help="--only kernels-*: how many kernels the table lists")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (so that a profiler lists them)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--design", default="filasun", choices=["filasun", "gorulorn", "demavik"], help="--only design: the design that runs beside Qwen2")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "filasun", "gorulorn", "demavik"],
+    ap.add_argument("--design", default="filasun", choices=["filasun", "gorulorn", "demavik", "pifazen"], help="--only design: the design that runs beside Qwen2")
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "filasun", "gorulorn", "demavik", "pifazen"],
                     help="which design the parts behind --only are measured on, with the layer sizes of --shape (default: the headline's Qwen2)")
     ap.add_argument("--design-shapes", default="1.5b,7b", help="--only design: the shapes whose layer sizes are run, with commas")
     args = ap.parse_args()
@@ -829,6 +860,13 @@ def main() -> int:
             print("bench.py: --arch demavik goes with --only decode|prefill|kernels-decode|kernels-prefill|design")
             return 2
         cfg = demavik_config(args.shape, args.layers or 6)
+        cfg["num_hidden_layers"], cfg["max_position_embeddings"] = len(cfg["layers"]), cfg["max_positions"]
+        cfg.update(num_key_value_heads=0, head_dim=0, hidden_size=cfg["width"])
+    if args.arch == "pifazen":
+        if args.only == "all":
+            print("bench.py: --arch pifazen goes with --only decode|prefill|kernels-decode|kernels-prefill|design")
+            return 2
+        cfg = pifazen_config(args.shape, args.layers or 6)
         cfg["num_hidden_layers"], cfg["max_position_embeddings"] = len(cfg["layers"]), cfg["max_positions"]
         cfg.update(num_key_value_heads=0, head_dim=0, hidden_size=cfg["width"])
     if args.only in ("decode", "kernels-decode") and args.context + 4096 > cfg["max_position_embeddings"]:

@@ -566,7 +566,8 @@ def test_gated_delta_rule_scan_kernel(heads, kv, d, dv, dtype):
     # one token at a time gives the same as the portion
     state2, out2 = ref_state.clone().copy_(0.3 * torch.randn_like(state)), torch.zeros_like(out)
     whole_state, whole = state2.clone(), torch.zeros_like(out)
-    K.delta_scan(qkv, 3, 3 + kv * d, 5 + 2 * kv * d, b, 2, za, 1, A_log, whole_state, q_start[:2].contiguous(), sl[:1].contiguous(), whole[:37], heads, kv, d, dv)
+    K.delta_scan(qkv[:37].contiguous(), 3, 3 + kv * d, 5 + 2 * kv * d, b[:37].contiguous(), 2, za[:37].contiguous(), 1, A_log, whole_state,
+                 q_start[:2].contiguous(), sl[:1].contiguous(), whole[:37], heads, kv, d, dv)
     for t in range(37):
         qs = torch.tensor([0, 1], dtype=torch.int32, device=dev)
         K.delta_scan(qkv[t:t + 1].contiguous(), 3, 3 + kv * d, 5 + 2 * kv * d, b[t:t + 1].contiguous(), 2, za[t:t + 1].contiguous(), 1, A_log, state2, qs,
