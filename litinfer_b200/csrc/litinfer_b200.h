@@ -174,14 +174,21 @@ int li_gla_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, in
     float inv_tau, float q_scale, float* state, long long state_stride, const int* q_start, const int* slots, float* out,
     int S, int heads, int d, int dv, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream);
 
-/* Per head S [d, dv] under the gated delta rule: S = diag(g) S, u = beta (v - S^T k), S = S + k u^T, out = S^T q.  q and k
- * (kv_heads of them, head h uses h / (heads / kv_heads)) at q_off, k_off of qkv [T, stride], made unit vectors here
- * (x / sqrt(sum x^2 + unit_eps), q times q_scale); v (heads x dv) at v_off; beta = sigmoid(b [T, b_stride] at b_off + h);
- * g = exp(-exp(A_log[h]) softplus(za [T, za_stride] at za_off + h d + i)), za float; the state is kept as [heads][dv][d]. */
-int li_delta_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const void* b, int b_stride, int b_off,
-    const float* za, int za_stride, int za_off, const float* A_log, float q_scale, float unit_eps, float* state,
-    long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv,
-    cudaStream_t stream);
+/* The gated delta rule, per head S [d, dv]: S = diag(g) S, u = beta (v - S^T k), S = S + k u^T, out = S^T q.  li_delta_prepare
+ * makes per token what does not depend on the state: the causal convolution (conv_w [channels, taps], older inputs from the
+ * state at state_off) and silu of the channels q | k | v (kv_heads d, kv_heads d, heads dv) at column col0 of proj [T, stride];
+ * q and k as unit vectors (x / sqrt(sum x^2 + unit_eps), q times q_scale) and k . q into prep_qk [T, kv_heads, 2 DP + 4];
+ * g = exp(-exp(A_log[h]) softplus(za [T, za_stride] at za_off + h d + i)) and beta = sigmoid(proj[b_off + h]) into prep_g
+ * [T, heads, DP + 4]; v [T, heads dv]; all float, DP = 32, 64, 128 or 256 (the first that holds d).  shift: every sequence has
+ * one token and the convolution's state moves on here.  li_delta_scan walks; head h uses key head h / (heads / kv_heads); the
+ * state is kept as [heads][dv][d]. */
+int li_delta_prepare(const void* proj, int dtype, int stride, int col0, int b_off, const float* conv_w, int taps, float* state,
+    long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
+    const float* za, int za_stride, int za_off, const float* A_log, float q_scale, float unit_eps, float* prep_qk,
+    float* prep_g, float* v, int T, int heads, int kv_heads, int d, int dv, int shift, cudaStream_t stream);
+void li_delta_force_warps(int warps);   /* 0: the walk's usual block size; 1, 2 or 4 warps a block, for measurements */
+int li_delta_scan(const float* prep_qk, const float* prep_g, const float* v, float* state, long long state_stride, const int* q_start,
+    const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv, cudaStream_t stream);
 
 /* Per channel c a state S [N]: S = exp(dt_c A[c, :]) S + dt_c x_c B, y_c = (S . C + D[c] x_c) silu(z_c), with
  * dt = softplus(dt_raw) (float, [T, dt_stride]), A = -exp(A_log) [inner, N]; x at column x_off of [T, x_stride], B and C

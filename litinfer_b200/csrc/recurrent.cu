@@ -15,8 +15,9 @@
 //     x / (1 + exp(-x)) on the way in.
 //   * li_gla_scan: per head a state S [d, dv] with a decay per token and key channel:  S = diag(a_t) S + k v^T,
 //     o = S^T (q / sqrt(d)),  a_t = sigmoid(z_t)^(1 / tau) from float logits z.
-//   * li_delta_scan: per head a state S [d, dv] under the gated delta rule with a decay per token and key channel:
-//     S = diag(g) S,  u = beta (v - S^T k),  S = S + k u^T,  o = S^T q, with q and k made unit vectors on the way in.
+//   * li_delta_prepare / li_delta_scan: per head a state S [d, dv] under the gated delta rule with a decay per token and key
+//     channel:  S = diag(g) S,  u = beta (v - S^T k),  S = S + k u^T,  o = S^T q; the first kernel makes what does not depend on
+//     the state (convolution, unit vectors q and k, decays, beta), the second walks.
 //   * li_channel_scan: a state S [N] per channel c with a decay per token, channel and element:
 //     S = exp(dt_c A[c, :]) S + dt_c x_c B,  y_c = (S . C + D_c x_c) silu(z_c),  dt = softplus(dt_raw), A = -exp(A_log).
 //   * li_gated_rmsnorm: RMSNorm in equal groups of a float row, with a gate before the norm (y * silu(z)) or after
@@ -459,29 +460,105 @@ gla_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int
 
 // The gated delta rule with a decay per token, head and key channel.  Per head a state S [d, dv]:
 //     S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t      (in this order: o sees the write)
-// A column of S moves on by itself here too (u[c] depends on column c alone), so the walk is the one of gla_scan_kernel:
-// a warp holds eight columns, each lane E neighbouring key channels of all eight.  The two sums over the key channels that
-// a token needs, (gS)^T k and (gS)^T q, are taken together before the write, since S_new^T q = (gS)^T q + u (k . q); k . q
-// is a number per token, taken while staging.  qk [T, stride]: q at column q_off + hk d, k at k_off + hk d with
-// hk = h / (heads / kv_heads), v at v_off + h dv, all after their convolution and activation; q and k are made unit
-// vectors here, x / sqrt(sum x^2 + unit_eps), and q is multiplied by q_scale.  beta = sigmoid(b[T, b_stride] at b_off + h);
-// g = exp(-exp(A_log[h]) softplus(za[T, za_stride] at za_off + h d + i)), za float (the map's bias already added).
-// All of that in float while staging.  One piece per sequence: the rule is not elementwise in S, so chunks of a portion do
-// not run side by side.
-template <typename T, int E>
-__global__ void __launch_bounds__(512)
-delta_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int v_off, const T* __restrict__ b, int b_stride, int b_off,
-                  const float* __restrict__ za, int za_stride, int za_off, const float* __restrict__ A_log, float q_scale, float unit_eps,
-                  float* __restrict__ state, long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
-                  float* __restrict__ out, int heads, int kv_heads, int d, int dv) {
+// Two kernels.  delta_prepare_kernel makes everything of a token that does not depend on the state, one warp per unit of
+// work, in float: for a key head the convolution and silu of its q and k channels, both made unit vectors
+// (x / sqrt(sum x^2 + unit_eps), q times q_scale) and k . q; for a head the decays g = exp(-exp(A_log[h]) softplus(za)) and
+// beta = sigmoid(b); for a head's values the convolution and silu.  Rows of DP = 32 E floats with zeros behind d, so that the
+// scan stages them as they are: prep_qk [T, kv_heads, 2 DP + 4] (q | k | k . q), prep_g [T, heads, DP + 4] (g | beta),
+// v [T, heads dv].  Every channel of the convolution belongs to one warp, which also moves the channel's state on in a step of
+// single tokens (`shift`).
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const T* __restrict__ proj, int stride, int col0, int b_off, const float* __restrict__ conv_w, int taps,
+                     float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
+                     const int* __restrict__ seq_of_token, const int* __restrict__ slots, const float* __restrict__ za, int za_stride, int za_off,
+                     const float* __restrict__ A_log, float q_scale, float unit_eps, float* __restrict__ prep_qk, float* __restrict__ prep_g,
+                     float* __restrict__ v_out, int total, int heads, int kv_heads, int d, int dv, int DP, int shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int units = kv_heads + 2 * heads;
+    const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (id >= (long long)total * units) return;
+    const int t = (int)(id / units), u = (int)(id - (long long)t * units);
+    const int lane = threadIdx.x & 31;
+    const int s = seq_of_token[t];
+    const int q0 = q_start[s], li = t - q0;
+    const int C = 2 * kv_heads * d + heads * dv;
+    float* st = state + (size_t)slots[s] * state_stride + state_off;
+    // channel c of the convolution for this token, with silu; the channel's state moves on if the step is one of single tokens
+    auto conv = [&](int c) {
+        float acc = 0.0f;
+        for (int k = 0; k < taps; ++k) {
+            const int i = li - (taps - 1) + k;
+            const float v = i >= 0 ? to_float(proj[(size_t)(q0 + i) * stride + col0 + c]) : st[(size_t)(taps - 1 + i) * C + c];
+            acc = fmaf(conv_w[(size_t)c * taps + k], v, acc);
+        }
+        if (shift)
+            for (int j = 0; j + 1 < taps; ++j)
+                st[(size_t)j * C + c] = j + 2 < taps ? st[(size_t)(j + 1) * C + c] : to_float(proj[(size_t)t * stride + col0 + c]);
+        return silu_f(acc);
+    };
+    if (u < kv_heads) {
+        float qv[8], kv[8];
+        float qq = 0.0f, kk = 0.0f, qk = 0.0f;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int i = lane + 32 * it;
+            qv[it] = i < d ? conv(u * d + i) : 0.0f;
+            kv[it] = i < d ? conv(kv_heads * d + u * d + i) : 0.0f;
+            qq = fmaf(qv[it], qv[it], qq); kk = fmaf(kv[it], kv[it], kk); qk = fmaf(qv[it], kv[it], qk);
+        }
+        qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
+        const float fq = q_scale / sqrtf(qq + unit_eps), fk = 1.0f / sqrtf(kk + unit_eps);
+        float* row = prep_qk + ((size_t)t * kv_heads + u) * (2 * DP + 4);
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int i = lane + 32 * it;
+            if (i < DP) {
+                row[i] = qv[it] * fq;
+                row[DP + i] = kv[it] * fk;
+            }
+        }
+        if (lane == 0) row[2 * DP] = qk * fq * fk;
+    } else if (u < kv_heads + heads) {
+        const int h = u - kv_heads;
+        const float rate = -expf(A_log[h]);
+        const float* zrow = za + (size_t)t * za_stride + za_off + h * d;
+        float* row = prep_g + ((size_t)t * heads + h) * (DP + 4);
+        for (int i = lane; i < DP; i += 32) row[i] = i < d ? expf(rate * softplus_f(zrow[i])) : 0.0f;
+        if (lane == 0) row[DP] = sigmoid_f(to_float(proj[(size_t)t * stride + b_off + h]));
+    } else {
+        const int h = u - kv_heads - heads;
+        for (int j = lane; j < dv; j += 32) v_out[(size_t)t * heads * dv + h * dv + j] = conv(2 * kv_heads * d + h * dv + j);
+    }
+}
+
+// The walk itself.  A column of S moves on by itself here too (u[c] depends on column c alone), so it is the walk of
+// gla_scan_kernel: a warp holds eight columns, each lane E neighbouring key channels of all eight.  The two sums over the key
+// channels that a token needs, (gS)^T k and (gS)^T q, are taken together before the write, since S_new^T q = (gS)^T q +
+// u (k . q).  A block has few warps (a head's columns are spread over many blocks: the walk is a chain of dependent
+// instructions per token, and a multiprocessor issues one warp's chain no faster when it holds sixteen of them) and stages the
+// prepared rows of kStage tokens as they are, the next stage's while it walks this one's.  One piece per sequence: the rule is not elementwise in S, so chunks of a portion
+// do not run side by side.
+// 16 bytes from global to shared memory without passing registers; zeros if not valid
+__device__ __forceinline__ void stage16(float* dst, const float* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes));
+}
+
+template <int E>
+__global__ void __launch_bounds__(128)
+delta_scan_kernel(const float* __restrict__ prep_qk, const float* __restrict__ prep_g, const float* __restrict__ vin, float* __restrict__ state,
+                  long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ out, int heads,
+                  int kv_heads, int d, int dv) {
     constexpr int DP = 32 * E;
     const int warps = blockDim.x >> 5, cols = kWarpCols * warps;
+    // two buffers of kStage tokens each: the next stage's rows are on their way (asynchronous copies of 16 bytes) while this
+    // stage is walked.  A buffer: q [kStage][DP] | k [kStage][DP] | decays [kStage][DP] | v [kStage][cols] | (beta ...) [kStage][4]
+    // | (k . q ...) [kStage][4]
     extern __shared__ __align__(16) float smem[];
-    float* qs = smem;                           // [kStage][DP]
-    float* ks = qs + kStage * DP;               // [kStage][DP]
-    float* as = ks + kStage * DP;               // [kStage][DP] decays
-    float* vs = as + kStage * DP;               // [kStage][cols]
-    float* sc = vs + kStage * cols;             // [kStage][2]: beta, k . q
+    const int buf_floats = 3 * kStage * DP + kStage * cols + 8 * kStage;
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.y;
@@ -489,53 +566,72 @@ delta_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, i
     const int q0 = q_start[blockIdx.z], q1 = q_start[blockIdx.z + 1];
     if (q1 <= q0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int col0 = blockIdx.x * cols + warp * kWarpCols;
+    const int block_col0 = blockIdx.x * cols;
+    const int col0 = block_col0 + warp * kWarpCols;
     float* st = state + (size_t)slots[blockIdx.z] * state_stride + (size_t)h * dv * d;
-    const float rate = -expf(A_log[h]);
+    constexpr int RQ = 2 * DP + 4, RG = DP + 4;
+    const bool v16 = (dv & 3) == 0 && (((uintptr_t)vin) & 15) == 0;          // the values' rows in pieces of 16 bytes
+    auto stage = [&](int b, int t0) {
+        float* qs = smem + (size_t)b * buf_floats;
+        float* ks = qs + kStage * DP;
+        float* as = ks + kStage * DP;
+        float* vs = as + kStage * DP;
+        float* sb = vs + kStage * cols;
+        float* sq = sb + 4 * kStage;
+        const int nt = min(kStage, q1 - t0);
+        for (int idx = threadIdx.x; idx < nt * (DP / 4); idx += blockDim.x) {
+            const int tk = idx / (DP / 4), i = idx - tk * (DP / 4);
+            const float* rq = prep_qk + ((size_t)(t0 + tk) * kv_heads + hk) * RQ;
+            const float* rg = prep_g + ((size_t)(t0 + tk) * heads + h) * RG;
+            stage16(qs + tk * DP + 4 * i, rq + 4 * i, true);
+            stage16(ks + tk * DP + 4 * i, rq + DP + 4 * i, true);
+            stage16(as + tk * DP + 4 * i, rg + 4 * i, true);
+        }
+        for (int tk = threadIdx.x; tk < nt; tk += blockDim.x) {
+            stage16(sb + 4 * tk, prep_g + ((size_t)(t0 + tk) * heads + h) * RG + DP, true);
+            stage16(sq + 4 * tk, prep_qk + ((size_t)(t0 + tk) * kv_heads + hk) * RQ + 2 * DP, true);
+        }
+        if (v16) {
+            for (int e = threadIdx.x; e < nt * (cols / 4); e += blockDim.x) {
+                const int tk = e / (cols / 4), j4 = e - tk * (cols / 4);
+                const int c = block_col0 + 4 * j4;
+                stage16(vs + tk * cols + 4 * j4, vin + (size_t)(t0 + tk) * heads * dv + h * dv + (c < dv ? c : 0), c < dv);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+                const int tk = e / cols, j = e - tk * cols;
+                const int c = block_col0 + j;
+                vs[e] = c < dv ? vin[(size_t)(t0 + tk) * heads * dv + h * dv + c] : 0.0f;
+            }
+        }
+        asm volatile("cp.async.commit_group;");
+    };
+    stage(0, q0);
     float S[kWarpCols][E];
 #pragma unroll
     for (int j = 0; j < kWarpCols; ++j)
 #pragma unroll
         for (int e = 0; e < E; ++e) S[j][e] = (col0 + j < dv && E * lane + e < d) ? st[(size_t)(col0 + j) * d + E * lane + e] : 0.0f;
-    for (int t0 = q0; t0 < q1; t0 += kStage) {
+    int b = 0;
+    for (int t0 = q0; t0 < q1; t0 += kStage, b ^= 1) {
         const int nt = min(kStage, q1 - t0);
-        __syncthreads();
-        for (int tk = warp; tk < nt; tk += warps) {
-            const T* row = qkv + (size_t)(t0 + tk) * stride;
-            const float* zrow = za + (size_t)(t0 + tk) * za_stride + za_off + h * d;
-            float qq = 0.0f, kk = 0.0f, qk = 0.0f;
-            for (int i = lane; i < DP; i += 32) {
-                const float qv = i < d ? to_float(row[q_off + hk * d + i]) : 0.0f;
-                const float kv = i < d ? to_float(row[k_off + hk * d + i]) : 0.0f;
-                qq = fmaf(qv, qv, qq); kk = fmaf(kv, kv, kk); qk = fmaf(qv, kv, qk);
-                qs[tk * DP + i] = qv;
-                ks[tk * DP + i] = kv;
-                as[tk * DP + i] = i < d ? expf(rate * softplus_f(zrow[i])) : 0.0f;
-            }
-            qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
-            const float fq = q_scale / sqrtf(qq + unit_eps), fk = 1.0f / sqrtf(kk + unit_eps);
-            for (int i = lane; i < DP; i += 32) {                     // (a lane scales what it wrote itself)
-                qs[tk * DP + i] *= fq;
-                ks[tk * DP + i] *= fk;
-            }
-            if (lane == 0) {
-                sc[2 * tk] = sigmoid_f(to_float(b[(size_t)(t0 + tk) * b_stride + b_off + h]));
-                sc[2 * tk + 1] = qk * fq * fk;
-            }
-        }
-        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
-            const int tk = e / cols, j = e - tk * cols;
-            const int c = blockIdx.x * cols + j;
-            vs[e] = c < dv ? to_float(qkv[(size_t)(t0 + tk) * stride + v_off + h * dv + c]) : 0.0f;
-        }
-        __syncthreads();
+        asm volatile("cp.async.wait_group 0;");
+        __syncthreads();                     // this stage has landed for everybody, and everybody has left the other buffer
+        if (t0 + kStage < q1) stage(b ^ 1, t0 + kStage);
+        const float* qs = smem + (size_t)b * buf_floats;
+        const float* ks = qs + kStage * DP;
+        const float* as = ks + kStage * DP;
+        const float* vs = as + kStage * DP;
+        const float* sb = vs + kStage * cols;
+        const float* sq = sb + 4 * kStage;
+#pragma unroll 2
         for (int tk = 0; tk < nt; ++tk) {
             float kk[E], aa[E], qq[E], v[kWarpCols], acck[kWarpCols], accq[kWarpCols];
             load_elements<E>(kk, ks + tk * DP + E * lane);
             load_elements<E>(aa, as + tk * DP + E * lane);
             load_elements<E>(qq, qs + tk * DP + E * lane);
             load_elements<kWarpCols>(v, vs + tk * cols + warp * kWarpCols);
-            const float beta = sc[2 * tk], kq = sc[2 * tk + 1];
+            const float beta = sb[4 * tk], kq = sq[4 * tk];
 #pragma unroll
             for (int j = 0; j < kWarpCols; ++j) {
                 acck[j] = accq[j] = 0.0f;
@@ -546,13 +642,13 @@ delta_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, i
                     accq[j] = fmaf(S[j][e], qq[e], accq[j]);
                 }
             }
-            const float sk = sum8_across_warp(acck, lane), sq = sum8_across_warp(accq, lane);
+            const float sk = sum8_across_warp(acck, lane), sqv = sum8_across_warp(accq, lane);
             const int jm = column_after_sum8(lane);                   // the column whose sums this lane holds now
             float vm = v[0];
 #pragma unroll
             for (int j = 1; j < kWarpCols; ++j) vm = jm == j ? v[j] : vm;
             const float um = beta * (vm - sk);
-            if ((lane & 3) == 0 && col0 + jm < dv) out[(size_t)(t0 + tk) * heads * dv + h * dv + col0 + jm] = fmaf(um, kq, sq);
+            if ((lane & 3) == 0 && col0 + jm < dv) out[(size_t)(t0 + tk) * heads * dv + h * dv + col0 + jm] = fmaf(um, kq, sqv);
 #pragma unroll
             for (int j = 0; j < kWarpCols; ++j) {
                 const float u = __shfl_sync(0xffffffffu, um, 16 * ((j >> 2) & 1) + 8 * ((j >> 1) & 1) + 4 * (j & 1));
@@ -1092,42 +1188,75 @@ LI_EXPORT int li_gla_scan(const void* qkv, int dtype, int stride, int q_off, int
 #undef LI_SCAN
 }
 
-template <typename T, int E>
-static int launch_delta(const void* qkv, int stride, int q_off, int k_off, int v_off, const void* b, int b_stride, int b_off, const float* za,
-                        int za_stride, int za_off, const float* A_log, float q_scale, float unit_eps, float* state, long long state_stride,
-                        const int* q_start, const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv, cudaStream_t stream) {
-    const int warps = scan_warps(dv), cols = warps * kWarpCols;
-    const size_t smem = ((size_t)3 * kStage * 32 * E + kStage * cols + 2 * kStage) * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaError_t e = li_launch_pdl(delta_scan_kernel<T, E>, dim3(ceil_div(dv, cols), heads, S), dim3(warps * 32), smem, stream, (const T*)qkv, stride,
-                                  q_off, k_off, v_off, (const T*)b, b_stride, b_off, za, za_stride, za_off, A_log, q_scale, unit_eps, state,
+// key channels a lane holds for keys of d elements (rows of the prepared vectors have 32 E floats)
+static int delta_elements(int d) { return d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8; }
+constexpr int kDeltaWarps = 2;          // warps of a block of the walk: sixteen columns
+static int g_delta_warps = 0;           // 0: kDeltaWarps; 1, 2 or 4: that many, for measurements
+
+template <int E>
+static int launch_delta(const float* prep_qk, const float* prep_g, const float* v, float* state, long long state_stride, const int* q_start,
+                        const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv, cudaStream_t stream) {
+    const int most = g_delta_warps > 0 ? g_delta_warps : kDeltaWarps;
+    const int warps = scan_warps(dv) < most ? scan_warps(dv) : most, cols = warps * kWarpCols;
+    const size_t smem = 2 * ((size_t)3 * kStage * 32 * E + kStage * cols + 8 * kStage) * sizeof(float);          // two buffers
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(delta_scan_kernel<E>, dim3(ceil_div(dv, cols), heads, S), dim3(warps * 32), smem, stream, prep_qk, prep_g, v, state,
                                   state_stride, q_start, slots, out, heads, kv_heads, d, dv);
     if (e != cudaSuccess) return li_fail("delta_scan: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("delta_scan");
 }
 
-// The state of a slot: [heads][dv][d] (a column of the head's d x dv matrix at a time).  See delta_scan_kernel.
-LI_EXPORT int li_delta_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const void* b, int b_stride, int b_off,
-                            const float* za, int za_stride, int za_off, const float* A_log, float q_scale, float unit_eps, float* state,
-                            long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv,
-                            cudaStream_t stream) {
+// What the walk of the gated delta rule needs of every token, from the projections (see delta_prepare_kernel).  proj [T, stride]
+// holds the convolution's channels q | k | v (kv_heads d, kv_heads d, heads dv) from column col0 and beta's input at b_off + h;
+// conv_w [channels, taps]; the state holds the last taps - 1 inputs at state_off ([taps - 1, channels], oldest first);
+// za [T, za_stride] float: the decays' input at za_off + h d + i.  Outputs: prep_qk [T, kv_heads, 2 DP + 4], prep_g
+// [T, heads, DP + 4], v [T, heads dv], float, with DP = 32, 64, 128 or 256 (the first that holds d).
+LI_EXPORT int li_delta_prepare(const void* proj, int dtype, int stride, int col0, int b_off, const float* conv_w, int taps, float* state,
+                               long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
+                               const float* za, int za_stride, int za_off, const float* A_log, float q_scale, float unit_eps, float* prep_qk,
+                               float* prep_g, float* v, int T, int heads, int kv_heads, int d, int dv, int shift, cudaStream_t stream) {
     LI_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && d > 0 && d <= 256 && dv > 0,
                "delta rule: %d heads on %d key heads of %d x %d (keys of at most 256)", heads, kv_heads, d, dv);
+    LI_REQUIRE(taps >= 1 && taps <= kMaxTaps && conv_w != nullptr, "delta rule: a convolution of %d taps (at most %d)", taps, kMaxTaps);
     LI_REQUIRE(za != nullptr && za_off >= 0 && za_off + heads * d <= za_stride, "delta rule: decays at column %d of %d", za_off, za_stride);
-    LI_REQUIRE(b != nullptr && b_off >= 0 && b_off + heads <= b_stride && A_log != nullptr, "delta rule: write strengths at column %d of %d", b_off, b_stride);
+    LI_REQUIRE(col0 >= 0 && col0 + 2 * kv_heads * d + heads * dv <= stride && b_off >= 0 && b_off + heads <= stride && A_log != nullptr,
+               "delta rule: the projections' columns do not fit rows of %d", stride);
     LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "delta rule: unknown dtype %d", dtype);
+    if (T == 0) return 0;
+    const int DP = 32 * delta_elements(d);
+    const long long warps = (long long)T * (kv_heads + 2 * heads);
+    const dim3 grid((unsigned)ceil_div_ll(warps, 4));
+    cudaError_t e;
+    if (dtype == LI_F32)
+        e = li_launch_pdl(delta_prepare_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, stride, col0, b_off, conv_w, taps, state,
+                          state_stride, state_off, q_start, seq_of_token, slots, za, za_stride, za_off, A_log, q_scale, unit_eps, prep_qk, prep_g, v, T,
+                          heads, kv_heads, d, dv, DP, shift);
+    else
+        e = li_launch_pdl(delta_prepare_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)proj, stride, col0, b_off, conv_w, taps, state,
+                          state_stride, state_off, q_start, seq_of_token, slots, za, za_stride, za_off, A_log, q_scale, unit_eps, prep_qk, prep_g, v, T,
+                          heads, kv_heads, d, dv, DP, shift);
+    if (e != cudaSuccess) return li_fail("delta_prepare: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("delta_prepare");
+}
+
+// 0: the walk's blocks have their usual number of warps; 1, 2 or 4: that many.  For tests and measurements.
+LI_EXPORT void li_delta_force_warps(int warps) { g_delta_warps = (warps == 1 || warps == 2 || warps == 4) ? warps : 0; }
+
+// The walk over what li_delta_prepare made.  The state of a slot: [heads][dv][d] (a column of the head's d x dv matrix at a time).
+LI_EXPORT int li_delta_scan(const float* prep_qk, const float* prep_g, const float* v, float* state, long long state_stride, const int* q_start,
+                            const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv, cudaStream_t stream) {
+    LI_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && d > 0 && d <= 256 && dv > 0,
+               "delta rule: %d heads on %d key heads of %d x %d (keys of at most 256)", heads, kv_heads, d, dv);
+    LI_REQUIRE(prep_qk != nullptr && prep_g != nullptr && v != nullptr && (uintptr_t)prep_qk % 16 == 0 && (uintptr_t)prep_g % 16 == 0,
+               "delta rule: the prepared rows are missing or not on a 16-byte boundary");
     if (S == 0) return 0;
     LI_REQUIRE(S <= 65535 && heads <= 65535, "delta rule: %d sequences or %d heads in one launch", S, heads);
-#define LI_SCAN(RR)                                                                                                                              \
-    return dtype == LI_F32 ? launch_delta<float, RR>(qkv, stride, q_off, k_off, v_off, b, b_stride, b_off, za, za_stride, za_off, A_log, q_scale, \
-                                                     unit_eps, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream)      \
-                           : launch_delta<bf16, RR>(qkv, stride, q_off, k_off, v_off, b, b_stride, b_off, za, za_stride, za_off, A_log, q_scale,  \
-                                                    unit_eps, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream)
-    if (d <= 32) { LI_SCAN(1); }
-    if (d <= 64) { LI_SCAN(2); }
-    if (d <= 128) { LI_SCAN(4); }
-    LI_SCAN(8);
-#undef LI_SCAN
+    switch (delta_elements(d)) {
+        case 1: return launch_delta<1>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+        case 2: return launch_delta<2>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+        case 4: return launch_delta<4>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+        default: return launch_delta<8>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+    }
 }
 
 template <typename T, int E>

@@ -805,30 +805,71 @@ def gla_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, za: torch.Te
     run(chunks.seg, chunks.count, 2, cstate, cdecay)
 
 
-def delta_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, b: torch.Tensor, b_col: int, za: torch.Tensor, za_col: int,
-               A_log: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, out32: torch.Tensor, heads: int,
-               kv_heads: int, dim: int, vdim: int, unit_eps: float = 1e-6) -> None:
-    """The gated delta rule with a decay per token, head and key channel, state ``S [dim, vdim]`` per head at the start of
-    ``state[slot]`` (kept column by column, ``[heads, vdim, dim]``): ``S = diag(g_t) S``; ``u = beta_t (v_t - S^T k_t)``;
-    ``S = S + k_t u^T``; ``out_t = S^T q_t``.  q and k (``kv_heads`` heads of ``dim``; head h uses ``h // (heads / kv_heads)``) are
-    the columns of ``qkv`` at ``q_col`` and ``k_col``, made unit vectors here (``x / sqrt(sum x^2 + unit_eps)``, q also times
-    ``dim^-1/2``); v (``heads`` of ``vdim``) at ``v_col``; ``beta = sigmoid(b[:, b_col + h])``;
-    ``g = exp(-exp(A_log[h]) softplus(za[:, za_col + h dim + i]))`` with ``za`` float32.  A sequence's tokens run in order,
-    in one piece."""
-    T = qkv.shape[0]
-    _need(qkv, "q|k|v")
-    _need(b, "write strengths", qkv.dtype)
+def delta_row_elements(dim: int) -> int:
+    """How many floats a prepared vector of ``dim`` key channels takes (32, 64, 128 or 256: zeros behind ``dim``)."""
+    if dim > 256:
+        raise KernelError(f"the delta rule takes keys of at most 256 elements, got {dim}")
+    return 32 if dim <= 32 else 64 if dim <= 64 else 128 if dim <= 128 else 256
+
+
+def delta_prepare(proj: torch.Tensor, col: int, b_col: int, conv_w: torch.Tensor, state: torch.Tensor, state_off: int, q_start: torch.Tensor,
+                  seq_of_token: torch.Tensor, slots: torch.Tensor, za: torch.Tensor, za_col: int, A_log: torch.Tensor, prep_qk: torch.Tensor,
+                  prep_g: torch.Tensor, v32: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, unit_eps: float = 1e-6,
+                  shift: bool = False) -> None:
+    """What the gated delta rule needs of every token and does not depend on the state.  ``proj`` [T, *] holds the channels
+    q | k | v (``kv_heads * dim``, ``kv_heads * dim``, ``heads * vdim``) from column ``col`` and beta's input at ``b_col + h``.
+    Each channel passes a causal convolution (``conv_w`` float32 [channels, taps], the last column the token's own; inputs
+    before a portion from ``state[slot, state_off:]`` as [taps - 1, channels], oldest first) and silu.  q and k become unit
+    vectors per key head (``x / sqrt(sum x^2 + unit_eps)``, q also times ``dim^-1/2``).  Written, all float32, with ``DP`` =
+    :func:`delta_row_elements`: ``prep_qk`` [T, kv_heads, 2 DP + 4] = (q | k | k . q), ``prep_g`` [T, heads, DP + 4] = (g | beta)
+    with ``g = exp(-exp(A_log[h]) softplus(za[:, za_col + h dim + i]))`` (``za`` float32) and ``beta = sigmoid(.)``, ``v32``
+    [T, heads * vdim].  The state is not changed (:func:`conv_state_shift` does that afterwards), unless ``shift``: the caller
+    promises that every sequence of the step has one token."""
+    T = proj.shape[0]
+    C = 2 * kv_heads * dim + heads * vdim
+    DP = delta_row_elements(dim)
+    _need(proj, "projections")
+    _need(conv_w, "convolution weight", torch.float32)
+    if conv_w.dim() != 2 or conv_w.shape[0] != C:
+        raise KernelError(f"delta_prepare: convolution weight of shape {tuple(conv_w.shape)} for {C} channels")
+    taps = conv_w.shape[1]
     _need(za, "decay inputs", torch.float32)
     _need(A_log, "A_log", torch.float32, (heads,))
+    _need(prep_qk, "prepared q and k", torch.float32, (T, kv_heads, 2 * DP + 4))
+    _need(prep_g, "prepared decays", torch.float32, (T, heads, DP + 4))
+    _need(v32, "prepared values", torch.float32, (T, heads * vdim))
+    _need(q_start, "q_start", torch.int32)
+    _need(seq_of_token, "seq_of_token", torch.int32, (T,))
+    _need(slots, "state slots", torch.int32)
+    st, stride, off = _state_args(state, state_off)
+    if state_off + (taps - 1) * C > state.shape[1] or za.shape[0] != T:
+        raise KernelError("delta_prepare: the state or the decays are too small")
+    _check(library().li_delta_prepare(_p(proj), _i(_dt(proj)), _i(proj.shape[1]), _i(int(col)), _i(int(b_col)), _p(conv_w), _i(taps), st, stride, off,
+                                      _p(q_start), _p(seq_of_token), _p(slots), _p(za), _i(za.shape[1]), _i(int(za_col)), _p(A_log),
+                                      _f(float(dim) ** -0.5), _f(float(unit_eps)), _p(prep_qk), _p(prep_g), _p(v32), _i(T), _i(heads), _i(kv_heads),
+                                      _i(dim), _i(vdim), _i(1 if shift else 0), _stream(v32)), "delta_prepare")
+
+
+def delta_scan(prep_qk: torch.Tensor, prep_g: torch.Tensor, v32: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
+               out32: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int) -> None:
+    """The gated delta rule with a decay per token, head and key channel over what :func:`delta_prepare` made, state
+    ``S [dim, vdim]`` per head at the start of ``state[slot]`` (kept column by column, ``[heads, vdim, dim]``):
+    ``S = diag(g_t) S``; ``u = beta_t (v_t - S^T k_t)``; ``S = S + k_t u^T``; ``out_t = S^T q_t``; head h uses the q and k of key
+    head ``h // (heads / kv_heads)``.  A sequence's tokens run in order, in one piece."""
+    T = v32.shape[0]
+    DP = delta_row_elements(dim)
+    _need(prep_qk, "prepared q and k", torch.float32, (T, kv_heads, 2 * DP + 4))
+    _need(prep_g, "prepared decays", torch.float32, (T, heads, DP + 4))
+    _need(v32, "prepared values", torch.float32, (T, heads * vdim))
     _need(out32, "scan output", torch.float32, (T, heads * vdim))
     S = q_start.shape[0] - 1
+    _need(q_start, "q_start", torch.int32)
     _need(slots, "state slots", torch.int32, (S,))
     st, stride, _ = _state_args(state, 0)
-    if heads * dim * vdim > state.shape[1] or za.shape[0] != T or b.shape[0] != T:
-        raise KernelError("delta_scan: the state, the decays or the write strengths are too small")
-    _check(library().li_delta_scan(_p(qkv), _i(_dt(qkv)), _i(qkv.shape[1]), _i(q_col), _i(k_col), _i(v_col), _p(b), _i(b.shape[1]), _i(b_col),
-                                   _p(za), _i(za.shape[1]), _i(za_col), _p(A_log), _f(float(dim) ** -0.5), _f(float(unit_eps)), st, stride,
-                                   _p(q_start), _p(slots), _p(out32), _i(S), _i(heads), _i(kv_heads), _i(dim), _i(vdim), _stream(out32)), "delta_scan")
+    if heads * dim * vdim > state.shape[1]:
+        raise KernelError("delta_scan: the state is too small")
+    _check(library().li_delta_scan(_p(prep_qk), _p(prep_g), _p(v32), st, stride, _p(q_start), _p(slots), _p(out32), _i(S), _i(heads), _i(kv_heads),
+                                   _i(dim), _i(vdim), _stream(out32)), "delta_scan")
 
 
 def channel_scan(x: torch.Tensor, x_col: int, bc: torch.Tensor, b_col: int, c_col: int, dt32: torch.Tensor, z: torch.Tensor, z_col: int,

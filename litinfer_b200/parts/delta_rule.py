@@ -17,9 +17,11 @@ one weight shared by the heads, multiplied by ``sigmoid(W_g2 (W_g1 h))`` (a low-
 Unit norms, beta, the decays with their softplus and exponentials, the state and every sum of the recurrence and of the
 norm are float32 (the decays' second product has a float32 result).  A request's state slot holds S of every head and,
 behind it, the last ``taps - 1`` inputs of the convolution; both move on by whatever the step holds of the request.
+The convolution's results stay float32 on their way into the recurrence.
 
 One product serves q | k | v | b | a1 | g1; the second products of the two low-rank maps read that row's columns through
-matrices with zero columns elsewhere, so nothing is copied.  The kernels find the step's sequences and their slots on the
+matrices with zero columns elsewhere, so nothing is copied.  What does not depend on the state (convolution, unit vectors,
+decays, beta) is made once per token by one kernel, the walk over the state is a second one.  The kernels find the step's sequences and their slots on the
 device, so steps of single tokens are replayed from a captured graph.  A portion runs in one piece, token after token:
 the rule is not elementwise in S (the correction mixes the key channels), so chunks of it do not run side by side.
 """
@@ -75,7 +77,7 @@ class GatedDeltaRule(Mixer):
         self.out = FusedLinear(prefix, [n.get("o", "o_proj")], vv, [self.hidden], False, dtype, suffixes=suffixes)
         self.conv_names = [prefix + n.get(k, k + "_proj") + str(spec.get("conv_suffix", ".conv")) for k in ("q", "k", "v")]
         self.names = {k: prefix + n.get(k, d) for k, d in (("dt_bias", "dt_bias"), ("A_log", "A_log"), ("norm", "norm.weight"))}
-        self.conv_w = self.conv_b = self.A_log = self.norm_weight = None
+        self.conv_w = self.A_log = self.norm_weight = None
         self.scan_elements = self.heads * self.dim * self.value_dim
 
     def params(self) -> List[ParamSpec]:
@@ -102,7 +104,6 @@ class GatedDeltaRule(Mixer):
         nm = self.names
         self.decay_out.bias = tensors.pop(nm["dt_bias"]).contiguous()            # the decays' map ends with this addition
         self.conv_w = torch.cat([tensors.pop(name) for name in self.conv_names], dim=0).contiguous()
-        self.conv_b = torch.zeros(self.channels, dtype=torch.float32, device=self.conv_w.device)
         self.A_log = tensors.pop(nm["A_log"]).contiguous()
         self.norm_weight = tensors.pop(nm["norm"]).repeat(self.heads).contiguous()
 
@@ -112,17 +113,20 @@ class GatedDeltaRule(Mixer):
     def forward(self, h, ctx, cache):
         T = h.shape[0]
         proj = self.proj(h)                                     # q | k | v | b | a1 | g1
-        qkv = torch.empty((T, self.channels), dtype=self.dtype, device=h.device)
-        single = ctx.max_q_len == 1                 # a step of single tokens: the convolution moves its state on itself
-        K.causal_conv_silu(proj, 0, self.conv_w, self.conv_b, cache.state, self.scan_elements, ctx.q_start, ctx.seq_of_token,
-                           ctx.state_slots, qkv, shift=single)
-        if not single and self.taps > 1:
-            K.conv_state_shift(proj, 0, self.channels, self.taps, cache.state, self.scan_elements, ctx.q_start, ctx.state_slots)
         za = self.decay_out(proj, out_dtype=torch.float32)      # the softplus' input, bias added
         gate = self.gate_out(proj)
+        # what does not depend on the state, once per token: convolution and silu, unit vectors, decays, beta
+        DP = K.delta_row_elements(self.dim)
+        prep_qk = torch.empty((T, self.kv_heads, 2 * DP + 4), dtype=torch.float32, device=h.device)
+        prep_g = torch.empty((T, self.heads, DP + 4), dtype=torch.float32, device=h.device)
+        v32 = torch.empty((T, self.vv), dtype=torch.float32, device=h.device)
+        single = ctx.max_q_len == 1                 # a step of single tokens: the convolution moves its state on itself
+        K.delta_prepare(proj, 0, self.b_col, self.conv_w, cache.state, self.scan_elements, ctx.q_start, ctx.seq_of_token, ctx.state_slots, za, 0,
+                        self.A_log, prep_qk, prep_g, v32, self.heads, self.kv_heads, self.dim, self.value_dim, UNIT_EPS, shift=single)
+        if not single and self.taps > 1:
+            K.conv_state_shift(proj, 0, self.channels, self.taps, cache.state, self.scan_elements, ctx.q_start, ctx.state_slots)
         o32 = torch.empty((T, self.vv), dtype=torch.float32, device=h.device)
-        K.delta_scan(qkv, 0, self.qk, 2 * self.qk, proj, self.b_col, za, 0, self.A_log, cache.state, ctx.q_start, ctx.state_slots, o32,
-                     self.heads, self.kv_heads, self.dim, self.value_dim, UNIT_EPS)
+        K.delta_scan(prep_qk, prep_g, v32, cache.state, ctx.q_start, ctx.state_slots, o32, self.heads, self.kv_heads, self.dim, self.value_dim)
         y = torch.empty((T, self.vv), dtype=self.dtype, device=h.device)
         K.gated_rmsnorm(o32, gate, 0, self.norm_weight, self.eps, self.heads, False, y, gate_act="sigmoid")
         return self.out(y)

@@ -127,6 +127,12 @@ class LatentAttention(Mixer):
         g = tensors.pop(self.names["dkv_norm"])
         if not self.plain:
             self.dkv_norm = g.contiguous()
+            w = self.down.weight
+            if w.shape[0] % 8:
+                # zero rows up to a multiple of 8: the products that read parts of this row find its rows on 16-byte boundaries
+                pad = -w.shape[0] % 8
+                self.down.weight = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)], dim=0).contiguous()
+                self.down.out_features = self.down.weight.shape[0]
         else:
             self.dkv_norm = torch.cat([g, torch.zeros(Rp - R, dtype=g.dtype, device=g.device)]).contiguous()
             if Rp != R:

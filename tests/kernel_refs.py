@@ -642,27 +642,63 @@ def latent_rope_post(low, col_c, col_r, q, dim, weight, eps, positions, denomina
     rows[:, :num_heads + 1, rank:rank + rot_dim] = res.to(out.dtype)
 
 
-def delta_scan(qkv, q_col, k_col, v_col, b, b_col, za, za_col, A_log, state, q_start, slots, out32, heads, kv_heads, dim, vdim, unit_eps=1e-6):
+def delta_row_elements(dim):
+    return 32 if dim <= 32 else 64 if dim <= 64 else 128 if dim <= 128 else 256
+
+
+def delta_prepare(proj, col, b_col, conv_w, state, state_off, q_start, seq_of_token, slots, za, za_col, A_log, prep_qk, prep_g, v32, heads, kv_heads,
+                  dim, vdim, unit_eps=1e-6, shift=False):
+    T = proj.shape[0]
+    C, taps = conv_w.shape
+    DP = delta_row_elements(dim)
+    starts, sl = q_start.tolist(), slots.tolist()
+    u = torch.zeros((T, C), dtype=torch.float32, device=proj.device)
+    x = proj[:, col:col + C].float()
+    for s in range(len(starts) - 1):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo:
+            continue
+        old = state[sl[s], state_off:state_off + (taps - 1) * C].view(taps - 1, C)
+        hist = torch.cat([old, x[lo:hi]], dim=0)
+        for k in range(taps):
+            u[lo:hi] += hist[k:k + hi - lo] * conv_w[:, k][None, :]
+        if shift and taps > 1:
+            old.copy_(hist[hi - lo:])
+    u = u * torch.sigmoid(u)
+    G = kv_heads
+    q, k, v = u[:, :G * dim].view(T, G, dim), u[:, G * dim:2 * G * dim].view(T, G, dim), u[:, 2 * G * dim:]
+    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * float(dim) ** -0.5
+    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+    prep_qk.zero_()
+    prep_qk[:, :, :dim] = q
+    prep_qk[:, :, DP:DP + dim] = k
+    prep_qk[:, :, 2 * DP] = (q * k).sum(-1)
+    prep_g.zero_()
+    sp = torch.nn.functional.softplus(za[:, za_col:za_col + heads * dim].float(), threshold=1e9).view(T, heads, dim)
+    prep_g[:, :, :dim] = torch.exp(-torch.exp(A_log)[None, :, None] * sp)
+    prep_g[:, :, DP] = torch.sigmoid(proj[:, b_col:b_col + heads].float())
+    v32.copy_(v)
+
+
+def delta_scan(prep_qk, prep_g, v32, state, q_start, slots, out32, heads, kv_heads, dim, vdim):
     starts, sl = q_start.tolist(), slots.tolist()
     rep = heads // kv_heads
+    DP = delta_row_elements(dim)
     for s in range(len(starts) - 1):
         lo, hi = starts[s], starts[s + 1]
         if hi == lo:
             continue
         S = state[sl[s], :heads * dim * vdim].view(heads, vdim, dim).transpose(1, 2)      # kept column by column: [heads][vdim][dim]
         for t in range(lo, hi):
-            row = qkv[t].float()
-            q = row[q_col:q_col + kv_heads * dim].view(kv_heads, dim)
-            k = row[k_col:k_col + kv_heads * dim].view(kv_heads, dim)
-            q = (q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * float(dim) ** -0.5).repeat_interleave(rep, dim=0)
-            k = (k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(rep, dim=0)
-            v = row[v_col:v_col + heads * vdim].view(heads, vdim)
-            beta = torch.sigmoid(b[t, b_col:b_col + heads].float())
-            g = torch.exp(-torch.exp(A_log)[:, None] * torch.nn.functional.softplus(za[t, za_col:za_col + heads * dim].float(), threshold=1e9).view(heads, dim))
+            q = prep_qk[t, :, :dim].repeat_interleave(rep, dim=0)
+            k = prep_qk[t, :, DP:DP + dim].repeat_interleave(rep, dim=0)
+            g, beta = prep_g[t, :, :dim], prep_g[t, :, DP]
+            v = v32[t].view(heads, vdim)
             S.mul_(g[:, :, None])
             u = beta[:, None] * (v - torch.einsum("hdv,hd->hv", S, k))
             S.add_(k[:, :, None] * u[:, None, :])
             out32[t] = torch.einsum("hdv,hd->hv", S, q).reshape(heads * vdim)
+
 
 def argmax(logits, out):
     # first maximum
@@ -753,7 +789,7 @@ def table_gather(resident, updates, slots, out, trash_page):
             out[s, b] = resident[slot, b] if b < cols else trash_page
 
 
-ALL = ["moe_route_grouped", "polynorm", "mul_sigmoid", "latent_rope_post", "delta_scan", "row_rinv", "add_pair_rows", "gla_scan", "channel_scan", "sorted_rows", "norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route", "moe_sort", "moe_gather", "moe_combine",
+ALL = ["moe_route_grouped", "polynorm", "mul_sigmoid", "latent_rope_post", "delta_prepare", "delta_scan", "delta_row_elements", "row_rinv", "add_pair_rows", "gla_scan", "channel_scan", "sorted_rows", "norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route", "moe_sort", "moe_gather", "moe_combine",
        "glu_clamped", "weighted_sum2", "add_position_rows", "hc_expand", "hc_read_norm", "hc_update", "causal_conv_silu", "conv_state_shift", "ssm_scan",
        "decay_scan", "gated_rmsnorm", "table_gather", "gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]

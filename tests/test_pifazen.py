@@ -541,8 +541,11 @@ def _sequences(lens, slots, dev):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv,d,dv", [(2, 2, 16, 8), (4, 2, 32, 40), (3, 1, 20, 17), (2, 1, 64, 64), (2, 2, 128, 72), (1, 1, 130, 9)])
-def test_gated_delta_rule_scan_kernel(heads, kv, d, dv, dtype):
+@pytest.mark.parametrize("heads,kv,d,dv,taps", [(2, 2, 16, 8, 3), (4, 2, 32, 40, 4), (3, 1, 20, 17, 1), (2, 1, 64, 64, 2), (2, 2, 128, 72, 4), (1, 1, 130, 9, 3)])
+def test_gated_delta_rule_kernels(heads, kv, d, dv, taps, dtype):
+    """The kernel that prepares a token (convolution, unit vectors, decays, beta) and the walk over the state, each against
+    its reference: shared key heads, an empty sequence, slots and tails of slots that nobody owns, a portion against its
+    tokens one by one (where the convolution's state moves on inside the first kernel)."""
     import kernel_refs as R
     from litinfer_b200 import kernels as K
 
@@ -551,29 +554,45 @@ def test_gated_delta_rule_scan_kernel(heads, kv, d, dv, dtype):
     lens, slots = [37, 1, 0, 18], [2, 0, 3, 1]
     T = sum(lens)
     q_start, sl = _sequences(lens, slots, dev)
-    width = 2 * kv * d + heads * dv + 5
-    qkv = torch.randn(T, width, device=dev).to(dt)
-    b = torch.randn(T, heads + 3, device=dev).to(dt)
+    seq = torch.tensor([s for s, n in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=dev)
+    C, S_el, DP = 2 * kv * d + heads * dv, heads * d * dv, K.delta_row_elements(d)
+    proj = torch.randn(T, 3 + C + heads + 5, device=dev).to(dt)
+    conv_w = (0.6 * torch.randn(C, taps, device=dev)).contiguous()
     za = (torch.randn(T, heads * d + 2, device=dev) - 2.0).contiguous()
     A_log = (0.5 * torch.randn(heads, device=dev) - 0.5).contiguous()
-    state = 0.3 * torch.randn(5, heads * d * dv + 11, device=dev)
-    ref_state, out, ref = state.clone(), torch.zeros(T, heads * dv, device=dev), torch.zeros(T, heads * dv, device=dev)
-    K.delta_scan(qkv, 3, 3 + kv * d, 5 + 2 * kv * d, b, 2, za, 1, A_log, state, q_start, sl, out, heads, kv, d, dv)
-    R.delta_scan(qkv, 3, 3 + kv * d, 5 + 2 * kv * d, b, 2, za, 1, A_log, ref_state, q_start, sl, ref, heads, kv, d, dv)
-    _close(out, ref, "float32", "outputs", 1e-4)
+    state = 0.3 * torch.randn(5, S_el + (taps - 1) * C + 11, device=dev)
+
+    def buffers(n):
+        return (torch.empty(n, kv, 2 * DP + 4, device=dev), torch.empty(n, heads, DP + 4, device=dev), torch.empty(n, heads * dv, device=dev))
+
+    got, ref = buffers(T), buffers(T)
+    K.delta_prepare(proj, 3, 3 + C + 1, conv_w, state, S_el, q_start, seq, sl, za, 1, A_log, *got, heads, kv, d, dv)
+    R.delta_prepare(proj, 3, 3 + C + 1, conv_w, state, S_el, q_start, seq, sl, za, 1, A_log, *ref, heads, kv, d, dv)
+    for a, b, what in zip(got, ref, ("q, k and their product", "decays and beta", "values")):
+        _close(a[..., :-3] if a.dim() == 3 else a, b[..., :-3] if b.dim() == 3 else b, "float32", what, 1e-5)
+    ref_state, out, want = state.clone(), torch.zeros(T, heads * dv, device=dev), torch.zeros(T, heads * dv, device=dev)
+    K.delta_scan(*got, state, q_start, sl, out, heads, kv, d, dv)
+    R.delta_scan(*ref, ref_state, q_start, sl, want, heads, kv, d, dv)
+    _close(out, want, "float32", "outputs", 1e-4)
     _close(state, ref_state, "float32", "states", 1e-4)
-    assert torch.equal(state[4], ref_state[4]) and torch.equal(state[:, heads * d * dv:], ref_state[:, heads * d * dv:]), "a slot or the tail of a slot that no sequence owns was touched"
-    # one token at a time gives the same as the portion
-    state2, out2 = ref_state.clone().copy_(0.3 * torch.randn_like(state)), torch.zeros_like(out)
-    whole_state, whole = state2.clone(), torch.zeros_like(out)
-    K.delta_scan(qkv[:37].contiguous(), 3, 3 + kv * d, 5 + 2 * kv * d, b[:37].contiguous(), 2, za[:37].contiguous(), 1, A_log, whole_state,
-                 q_start[:2].contiguous(), sl[:1].contiguous(), whole[:37], heads, kv, d, dv)
+    assert torch.equal(state[4], ref_state[4]) and torch.equal(state[:, S_el:], ref_state[:, S_el:]), "a slot or the tail of a slot that no sequence owns was touched"
+    # the first sequence again, one token at a time, from the state it had: the same outputs, and the convolution's inputs kept
+    one_state, outs = ref_state.clone().copy_(0.3 * torch.randn_like(state)), torch.zeros(37, heads * dv, device=dev)
+    whole_state, whole = one_state.clone(), torch.zeros(37, heads * dv, device=dev)
+    first = buffers(37)
+    qs37, sl1 = q_start[:2].contiguous(), sl[:1].contiguous()
+    K.delta_prepare(proj[:37].contiguous(), 3, 3 + C + 1, conv_w, whole_state, S_el, qs37, seq[:37].contiguous(), sl1, za[:37].contiguous(), 1, A_log, *first, heads, kv, d, dv)
+    if taps > 1:
+        K.conv_state_shift(proj[:37].contiguous(), 3, C, taps, whole_state, S_el, qs37, sl1)
+    K.delta_scan(*first, whole_state, qs37, sl1, whole, heads, kv, d, dv)
+    qs1, seq1 = torch.tensor([0, 1], dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
     for t in range(37):
-        qs = torch.tensor([0, 1], dtype=torch.int32, device=dev)
-        K.delta_scan(qkv[t:t + 1].contiguous(), 3, 3 + kv * d, 5 + 2 * kv * d, b[t:t + 1].contiguous(), 2, za[t:t + 1].contiguous(), 1, A_log, state2, qs,
-                     sl[:1].contiguous(), out2[t:t + 1], heads, kv, d, dv)
-    _close(out2[:37], whole[:37], "float32", "token by token against the portion", 1e-4)
-    _close(state2, whole_state, "float32", "states token by token", 1e-4)
+        step = buffers(1)
+        K.delta_prepare(proj[t:t + 1].contiguous(), 3, 3 + C + 1, conv_w, one_state, S_el, qs1, seq1, sl1, za[t:t + 1].contiguous(), 1, A_log, *step, heads, kv, d, dv,
+                        shift=True)
+        K.delta_scan(*step, one_state, qs1, sl1, outs[t:t + 1], heads, kv, d, dv)
+    _close(outs, whole, "float32", "token by token against the portion", 1e-4)
+    _close(one_state, whole_state, "float32", "states and convolution inputs token by token", 1e-4)
 
 
 @pytest.mark.gpu
