@@ -186,7 +186,7 @@ int li_delta_prepare(const void* proj, int dtype, int stride, int col0, int b_of
     long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
     const float* za, int za_stride, int za_off, const float* A_log, float q_scale, float unit_eps, float* prep_qk,
     float* prep_g, float* v, int T, int heads, int kv_heads, int d, int dv, int shift, cudaStream_t stream);
-void li_delta_force_warps(int warps);   /* 0: the walk's usual block size; 1, 2 or 4 warps a block, for measurements */
+void li_delta_force_columns(int columns);   /* 0: columns a warp of the walk by the launch's size; 2, 4 or 8, for tests and measurements */
 int li_delta_scan(const float* prep_qk, const float* prep_g, const float* v, float* state, long long state_stride, const int* q_start,
     const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv, cudaStream_t stream);
 

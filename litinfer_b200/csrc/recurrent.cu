@@ -154,6 +154,47 @@ __device__ __forceinline__ float sum8_across_warp(const float (&a)[8], int lane)
 }
 __device__ __forceinline__ int column_after_sum8(int lane) { return 4 * ((lane >> 4) & 1) + 2 * ((lane >> 3) & 1) + ((lane >> 2) & 1); }
 
+// The same for N = 8, 4 or 2 values a lane; the exchanges come in the same order (lanes 16, 8, 4, 2, 1 apart), so a column's sum
+// is the same bits whichever N carries it.  column_after_sum<N>: whose sum a lane holds; lane_of_column<N>: the first lane that
+// holds a column's; sum_is_first<N>: whether this lane is that one.
+template <int N>
+__device__ __forceinline__ float sum_across_warp(const float (&a)[N], int lane) {
+    if constexpr (N == 8) {
+        return sum8_across_warp(a, lane);
+    } else if constexpr (N == 4) {
+        float b[2];
+        const bool up16 = lane & 16, up8 = lane & 8;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) b[j] = (up16 ? a[j + 2] : a[j]) + __shfl_xor_sync(0xffffffffu, up16 ? a[j] : a[j + 2], 16);
+        float v = (up8 ? b[1] : b[0]) + __shfl_xor_sync(0xffffffffu, up8 ? b[0] : b[1], 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        return v + __shfl_xor_sync(0xffffffffu, v, 1);
+    } else {
+        static_assert(N == 2, "eight, four or two values a lane");
+        const bool up16 = lane & 16;
+        float v = (up16 ? a[1] : a[0]) + __shfl_xor_sync(0xffffffffu, up16 ? a[0] : a[1], 16);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        return v + __shfl_xor_sync(0xffffffffu, v, 1);
+    }
+}
+template <int N>
+__device__ __forceinline__ int column_after_sum(int lane) {
+    if constexpr (N == 8) return column_after_sum8(lane);
+    else if constexpr (N == 4) return 2 * ((lane >> 4) & 1) + ((lane >> 3) & 1);
+    else return (lane >> 4) & 1;
+}
+template <int N>
+__device__ __forceinline__ int lane_of_column(int j) {
+    if constexpr (N == 8) return 16 * ((j >> 2) & 1) + 8 * ((j >> 1) & 1) + 4 * (j & 1);
+    else if constexpr (N == 4) return 16 * ((j >> 1) & 1) + 8 * (j & 1);
+    else return 16 * (j & 1);
+}
+template <int N>
+__device__ __forceinline__ bool sum_is_first(int lane) { return (lane & (N == 8 ? 3 : N == 4 ? 7 : 15)) == 0; }
+
 // xbc [T, C]: x (heads * P) | B (groups * N) | C (groups * N), after convolution and activation.  E = ceil(N / 32)
 // rounded up to 1, 2, 4 or 8 elements a lane; blockDim.x / 32 warps of eight columns each.
 template <typename T, int E>
@@ -467,15 +508,17 @@ gla_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int
 // scan stages them as they are: prep_qk [T, kv_heads, 2 DP + 4] (q | k | k . q), prep_g [T, heads, DP + 4] (g | beta),
 // v [T, heads dv].  Every channel of the convolution belongs to one warp, which also moves the channel's state on in a step of
 // single tokens (`shift`).
-template <typename T>
+// TAPS: the taps at compile time (their loads are then all in flight at once), or 0: any number, at run time.
+template <typename T, int TAPS>
 __global__ void __launch_bounds__(128)
-delta_prepare_kernel(const T* __restrict__ proj, int stride, int col0, int b_off, const float* __restrict__ conv_w, int taps,
+delta_prepare_kernel(const T* __restrict__ proj, int stride, int col0, int b_off, const float* __restrict__ conv_w, int taps_rt,
                      float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
                      const int* __restrict__ seq_of_token, const int* __restrict__ slots, const float* __restrict__ za, int za_stride, int za_off,
                      const float* __restrict__ A_log, float q_scale, float unit_eps, float* __restrict__ prep_qk, float* __restrict__ prep_g,
                      float* __restrict__ v_out, int total, int heads, int kv_heads, int d, int dv, int DP, int shift) {
     pdl_launch_dependents();
     pdl_wait();
+    const int taps = TAPS > 0 ? TAPS : taps_rt;
     const int units = kv_heads + 2 * heads;
     const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (id >= (long long)total * units) return;
@@ -488,7 +531,8 @@ delta_prepare_kernel(const T* __restrict__ proj, int stride, int col0, int b_off
     // channel c of the convolution for this token, with silu; the channel's state moves on if the step is one of single tokens
     auto conv = [&](int c) {
         float acc = 0.0f;
-        for (int k = 0; k < taps; ++k) {
+#pragma unroll
+        for (int k = 0; k < (TAPS > 0 ? TAPS : taps); ++k) {
             const int i = li - (taps - 1) + k;
             const float v = i >= 0 ? to_float(proj[(size_t)(q0 + i) * stride + col0 + c]) : st[(size_t)(taps - 1 + i) * C + c];
             acc = fmaf(conv_w[(size_t)c * taps + k], v, acc);
@@ -534,8 +578,9 @@ delta_prepare_kernel(const T* __restrict__ proj, int stride, int col0, int b_off
 }
 
 // The walk itself.  A column of S moves on by itself here too (u[c] depends on column c alone), so it is the walk of
-// gla_scan_kernel: a warp holds eight columns, each lane E neighbouring key channels of all eight.  The two sums over the key
-// channels that a token needs, (gS)^T k and (gS)^T q, are taken together before the write, since S_new^T q = (gS)^T q +
+// gla_scan_kernel: a warp holds WC columns (eight, four or two), each lane E neighbouring key channels of all of them; with few
+// sequences and heads the columns are spread over more warps, since a token's chain of instructions is as long as its warp has
+// columns.  The two sums over the key channels that a token needs, (gS)^T k and (gS)^T q, are taken together before the write, since S_new^T q = (gS)^T q +
 // u (k . q).  A block has few warps (a head's columns are spread over many blocks: the walk is a chain of dependent
 // instructions per token, and a multiprocessor issues one warp's chain no faster when it holds sixteen of them) and stages the
 // prepared rows of kStage tokens as they are, the next stage's while it walks this one's.  One piece per sequence: the rule is not elementwise in S, so chunks of a portion
@@ -547,13 +592,13 @@ __device__ __forceinline__ void stage16(float* dst, const float* src, bool valid
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes));
 }
 
-template <int E>
+template <int E, int WC>
 __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ prep_qk, const float* __restrict__ prep_g, const float* __restrict__ vin, float* __restrict__ state,
                   long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ out, int heads,
                   int kv_heads, int d, int dv) {
     constexpr int DP = 32 * E;
-    const int warps = blockDim.x >> 5, cols = kWarpCols * warps;
+    const int warps = blockDim.x >> 5, cols = WC * warps;
     // two buffers of kStage tokens each: the next stage's rows are on their way (asynchronous copies of 16 bytes) while this
     // stage is walked.  A buffer: q [kStage][DP] | k [kStage][DP] | decays [kStage][DP] | v [kStage][cols] | (beta ...) [kStage][4]
     // | (k . q ...) [kStage][4]
@@ -567,10 +612,10 @@ delta_scan_kernel(const float* __restrict__ prep_qk, const float* __restrict__ p
     if (q1 <= q0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int block_col0 = blockIdx.x * cols;
-    const int col0 = block_col0 + warp * kWarpCols;
+    const int col0 = block_col0 + warp * WC;
     float* st = state + (size_t)slots[blockIdx.z] * state_stride + (size_t)h * dv * d;
     constexpr int RQ = 2 * DP + 4, RG = DP + 4;
-    const bool v16 = (dv & 3) == 0 && (((uintptr_t)vin) & 15) == 0;          // the values' rows in pieces of 16 bytes
+    const bool v16 = (dv & 3) == 0 && (cols & 3) == 0 && (((uintptr_t)vin) & 15) == 0;          // the values' rows in pieces of 16 bytes
     auto stage = [&](int b, int t0) {
         float* qs = smem + (size_t)b * buf_floats;
         float* ks = qs + kStage * DP;
@@ -607,9 +652,9 @@ delta_scan_kernel(const float* __restrict__ prep_qk, const float* __restrict__ p
         asm volatile("cp.async.commit_group;");
     };
     stage(0, q0);
-    float S[kWarpCols][E];
+    float S[WC][E];
 #pragma unroll
-    for (int j = 0; j < kWarpCols; ++j)
+    for (int j = 0; j < WC; ++j)
 #pragma unroll
         for (int e = 0; e < E; ++e) S[j][e] = (col0 + j < dv && E * lane + e < d) ? st[(size_t)(col0 + j) * d + E * lane + e] : 0.0f;
     int b = 0;
@@ -626,14 +671,14 @@ delta_scan_kernel(const float* __restrict__ prep_qk, const float* __restrict__ p
         const float* sq = sb + 4 * kStage;
 #pragma unroll 2
         for (int tk = 0; tk < nt; ++tk) {
-            float kk[E], aa[E], qq[E], v[kWarpCols], acck[kWarpCols], accq[kWarpCols];
+            float kk[E], aa[E], qq[E], v[WC], acck[WC], accq[WC];
             load_elements<E>(kk, ks + tk * DP + E * lane);
             load_elements<E>(aa, as + tk * DP + E * lane);
             load_elements<E>(qq, qs + tk * DP + E * lane);
-            load_elements<kWarpCols>(v, vs + tk * cols + warp * kWarpCols);
+            load_elements<WC>(v, vs + tk * cols + warp * WC);
             const float beta = sb[4 * tk], kq = sq[4 * tk];
 #pragma unroll
-            for (int j = 0; j < kWarpCols; ++j) {
+            for (int j = 0; j < WC; ++j) {
                 acck[j] = accq[j] = 0.0f;
 #pragma unroll
                 for (int e = 0; e < E; ++e) {
@@ -642,23 +687,23 @@ delta_scan_kernel(const float* __restrict__ prep_qk, const float* __restrict__ p
                     accq[j] = fmaf(S[j][e], qq[e], accq[j]);
                 }
             }
-            const float sk = sum8_across_warp(acck, lane), sqv = sum8_across_warp(accq, lane);
-            const int jm = column_after_sum8(lane);                   // the column whose sums this lane holds now
+            const float sk = sum_across_warp<WC>(acck, lane), sqv = sum_across_warp<WC>(accq, lane);
+            const int jm = column_after_sum<WC>(lane);                   // the column whose sums this lane holds now
             float vm = v[0];
 #pragma unroll
-            for (int j = 1; j < kWarpCols; ++j) vm = jm == j ? v[j] : vm;
+            for (int j = 1; j < WC; ++j) vm = jm == j ? v[j] : vm;
             const float um = beta * (vm - sk);
-            if ((lane & 3) == 0 && col0 + jm < dv) out[(size_t)(t0 + tk) * heads * dv + h * dv + col0 + jm] = fmaf(um, kq, sqv);
+            if (sum_is_first<WC>(lane) && col0 + jm < dv) out[(size_t)(t0 + tk) * heads * dv + h * dv + col0 + jm] = fmaf(um, kq, sqv);
 #pragma unroll
-            for (int j = 0; j < kWarpCols; ++j) {
-                const float u = __shfl_sync(0xffffffffu, um, 16 * ((j >> 2) & 1) + 8 * ((j >> 1) & 1) + 4 * (j & 1));
+            for (int j = 0; j < WC; ++j) {
+                const float u = __shfl_sync(0xffffffffu, um, lane_of_column<WC>(j));
 #pragma unroll
                 for (int e = 0; e < E; ++e) S[j][e] = fmaf(kk[e], u, S[j][e]);
             }
         }
     }
 #pragma unroll
-    for (int j = 0; j < kWarpCols; ++j)
+    for (int j = 0; j < WC; ++j)
 #pragma unroll
         for (int e = 0; e < E; ++e)
             if (col0 + j < dv && E * lane + e < d) st[(size_t)(col0 + j) * d + E * lane + e] = S[j][e];
@@ -1190,20 +1235,39 @@ LI_EXPORT int li_gla_scan(const void* qkv, int dtype, int stride, int q_off, int
 
 // key channels a lane holds for keys of d elements (rows of the prepared vectors have 32 E floats)
 static int delta_elements(int d) { return d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8; }
-constexpr int kDeltaWarps = 2;          // warps of a block of the walk: sixteen columns
-static int g_delta_warps = 0;           // 0: kDeltaWarps; 1, 2 or 4: that many, for measurements
+constexpr int kDeltaWarps = 4;          // warps of a block of the walk at most
+static int g_delta_cols = 0;            // 0: columns a warp by the size of the launch; 2, 4 or 8: that many, for tests and measurements
 
-template <int E>
+template <int E, int WC>
 static int launch_delta(const float* prep_qk, const float* prep_g, const float* v, float* state, long long state_stride, const int* q_start,
                         const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv, cudaStream_t stream) {
-    const int most = g_delta_warps > 0 ? g_delta_warps : kDeltaWarps;
-    const int warps = scan_warps(dv) < most ? scan_warps(dv) : most, cols = warps * kWarpCols;
+    int warps = ceil_div(dv, WC);
+    warps = warps >= kDeltaWarps ? kDeltaWarps : warps >= 2 ? 2 : 1;
+    const int cols = warps * WC;
     const size_t smem = 2 * ((size_t)3 * kStage * 32 * E + kStage * cols + 8 * kStage) * sizeof(float);          // two buffers
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaError_t e = li_launch_pdl(delta_scan_kernel<E>, dim3(ceil_div(dv, cols), heads, S), dim3(warps * 32), smem, stream, prep_qk, prep_g, v, state,
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<E, WC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(delta_scan_kernel<E, WC>, dim3(ceil_div(dv, cols), heads, S), dim3(warps * 32), smem, stream, prep_qk, prep_g, v, state,
                                   state_stride, q_start, slots, out, heads, kv_heads, d, dv);
     if (e != cudaSuccess) return li_fail("delta_scan: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("delta_scan");
+}
+
+// Columns a warp: as few as keep the launch at about two warps a scheduler (148 multiprocessors of four), at most eight.  The
+// result does not depend on it (sum_across_warp).
+static int delta_cols(int S, int heads, int dv) {
+    if (g_delta_cols) return g_delta_cols;
+    const long long columns = (long long)S * heads * dv;
+    return columns / 8 >= 1184 ? 8 : columns / 4 >= 1184 ? 4 : 2;
+}
+
+template <int E>
+static int launch_delta_cols(const float* prep_qk, const float* prep_g, const float* v, float* state, long long state_stride, const int* q_start,
+                             const int* slots, float* out, int S, int heads, int kv_heads, int d, int dv, cudaStream_t stream) {
+    switch (delta_cols(S, heads, dv)) {
+        case 8: return launch_delta<E, 8>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+        case 4: return launch_delta<E, 4>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+        default: return launch_delta<E, 2>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+    }
 }
 
 // What the walk of the gated delta rule needs of every token, from the projections (see delta_prepare_kernel).  proj [T, stride]
@@ -1227,20 +1291,28 @@ LI_EXPORT int li_delta_prepare(const void* proj, int dtype, int stride, int col0
     const long long warps = (long long)T * (kv_heads + 2 * heads);
     const dim3 grid((unsigned)ceil_div_ll(warps, 4));
     cudaError_t e;
-    if (dtype == LI_F32)
-        e = li_launch_pdl(delta_prepare_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, stride, col0, b_off, conv_w, taps, state,
-                          state_stride, state_off, q_start, seq_of_token, slots, za, za_stride, za_off, A_log, q_scale, unit_eps, prep_qk, prep_g, v, T,
-                          heads, kv_heads, d, dv, DP, shift);
-    else
-        e = li_launch_pdl(delta_prepare_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)proj, stride, col0, b_off, conv_w, taps, state,
-                          state_stride, state_off, q_start, seq_of_token, slots, za, za_stride, za_off, A_log, q_scale, unit_eps, prep_qk, prep_g, v, T,
-                          heads, kv_heads, d, dv, DP, shift);
+#define LI_PREPARE(TT, TAPS_)                                                                                                                  \
+    e = li_launch_pdl(delta_prepare_kernel<TT, TAPS_>, grid, dim3(128), 0, stream, (const TT*)proj, stride, col0, b_off, conv_w, taps, state,     \
+                      state_stride, state_off, q_start, seq_of_token, slots, za, za_stride, za_off, A_log, q_scale, unit_eps, prep_qk, prep_g, v, T, \
+                      heads, kv_heads, d, dv, DP, shift)
+    if (dtype == LI_F32) {
+        if (taps == 4) LI_PREPARE(float, 4);
+        else if (taps == 3) LI_PREPARE(float, 3);
+        else if (taps == 2) LI_PREPARE(float, 2);
+        else LI_PREPARE(float, 0);
+    } else {
+        if (taps == 4) LI_PREPARE(bf16, 4);
+        else if (taps == 3) LI_PREPARE(bf16, 3);
+        else if (taps == 2) LI_PREPARE(bf16, 2);
+        else LI_PREPARE(bf16, 0);
+    }
+#undef LI_PREPARE
     if (e != cudaSuccess) return li_fail("delta_prepare: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("delta_prepare");
 }
 
-// 0: the walk's blocks have their usual number of warps; 1, 2 or 4: that many.  For tests and measurements.
-LI_EXPORT void li_delta_force_warps(int warps) { g_delta_warps = (warps == 1 || warps == 2 || warps == 4) ? warps : 0; }
+// 0: columns a warp of the walk by the size of the launch; 2, 4 or 8: that many.  For tests and measurements.
+LI_EXPORT void li_delta_force_columns(int columns) { g_delta_cols = (columns == 2 || columns == 4 || columns == 8) ? columns : 0; }
 
 // The walk over what li_delta_prepare made.  The state of a slot: [heads][dv][d] (a column of the head's d x dv matrix at a time).
 LI_EXPORT int li_delta_scan(const float* prep_qk, const float* prep_g, const float* v, float* state, long long state_stride, const int* q_start,
@@ -1252,10 +1324,10 @@ LI_EXPORT int li_delta_scan(const float* prep_qk, const float* prep_g, const flo
     if (S == 0) return 0;
     LI_REQUIRE(S <= 65535 && heads <= 65535, "delta rule: %d sequences or %d heads in one launch", S, heads);
     switch (delta_elements(d)) {
-        case 1: return launch_delta<1>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
-        case 2: return launch_delta<2>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
-        case 4: return launch_delta<4>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
-        default: return launch_delta<8>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+        case 1: return launch_delta_cols<1>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+        case 2: return launch_delta_cols<2>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+        case 4: return launch_delta_cols<4>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
+        default: return launch_delta_cols<8>(prep_qk, prep_g, v, state, state_stride, q_start, slots, out, S, heads, kv_heads, d, dv, stream);
     }
 }
 

@@ -76,7 +76,15 @@ def test_rope_part_table_and_refusals():
     j = torch.arange(24, dtype=torch.float32)
     assert torch.allclose(rope.denominators.cpu(), torch.pow(torch.tensor(50000.0), 2 * j / 48))
     with pytest.raises(ValueError, match="pairing"):
-        POSITIONS.build(PartSpec("rope", {"theta": 1e4, "rotary_dim": 16, "pairing": "interleaved"}), "", torch.float32, DEV, head_dim=16)
+        POSITIONS.build(PartSpec("rope", {"theta": 1e4, "rotary_dim": 16, "pairing": "quarters"}), "", torch.float32, DEV, head_dim=16)
+    # pairs of neighbours are a pairing of the part; the paged attention part, whose kernels rotate halves, refuses it
+    near = PartSpec("rope", {"theta": 1e4, "rotary_dim": 16, "pairing": "interleaved"})
+    assert POSITIONS.build(near, "", torch.float32, DEV, head_dim=16).interleaved
+    from litinfer_b200.parts import MIXERS
+
+    with pytest.raises(ValueError, match="rotate halves"):
+        MIXERS.build(PartSpec("attention", {"hidden_size": 32, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "scale": 0.25, "position": near}),
+                     "", torch.float32, DEV)
     with pytest.raises(ValueError, match="rotary_dim"):
         POSITIONS.build(PartSpec("rope", {"theta": 1e4, "rotary_dim": 32}), "", torch.float32, DEV, head_dim=16)
 

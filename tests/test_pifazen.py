@@ -571,11 +571,22 @@ def test_gated_delta_rule_kernels(heads, kv, d, dv, taps, dtype):
     for a, b, what in zip(got, ref, ("q, k and their product", "decays and beta", "values")):
         _close(a[..., :-3] if a.dim() == 3 else a, b[..., :-3] if b.dim() == 3 else b, "float32", what, 1e-5)
     ref_state, out, want = state.clone(), torch.zeros(T, heads * dv, device=dev), torch.zeros(T, heads * dv, device=dev)
+    state0 = state.clone()
     K.delta_scan(*got, state, q_start, sl, out, heads, kv, d, dv)
     R.delta_scan(*ref, ref_state, q_start, sl, want, heads, kv, d, dv)
     _close(out, want, "float32", "outputs", 1e-4)
     _close(state, ref_state, "float32", "states", 1e-4)
     assert torch.equal(state[4], ref_state[4]) and torch.equal(state[:, S_el:], ref_state[:, S_el:]), "a slot or the tail of a slot that no sequence owns was touched"
+    # a warp of the walk holds two, four or eight columns, by the size of the launch: the same bits whichever it is
+    import ctypes
+    try:
+        for columns in (2, 4, 8):
+            K.library().li_delta_force_columns(ctypes.c_int(columns))
+            again_state, again = state0.clone(), torch.zeros_like(out)
+            K.delta_scan(*got, again_state, q_start, sl, again, heads, kv, d, dv)
+            assert torch.equal(again, out) and torch.equal(again_state, state), f"{columns} columns a warp"
+    finally:
+        K.library().li_delta_force_columns(ctypes.c_int(0))
     # the first sequence again, one token at a time, from the state it had: the same outputs, and the convolution's inputs kept
     one_state, outs = ref_state.clone().copy_(0.3 * torch.randn_like(state)), torch.zeros(37, heads * dv, device=dev)
     whole_state, whole = one_state.clone(), torch.zeros(37, heads * dv, device=dev)
