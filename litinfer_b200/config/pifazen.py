@@ -87,8 +87,10 @@ class PifazenConfig:
         new = []
         for i, layer in enumerate(layers):
             if isinstance(layer, Mapping) and layer.get("type") == "channel_delta" and isinstance(layer.get("mixer"), Mapping):
-                src = layer.get("weights_of")
-                j = src if isinstance(src, int) and not isinstance(src, bool) else i
+                j, hops = i, 0
+                while isinstance(layers[j], Mapping) and isinstance(layers[j].get("weights_of"), int) and not isinstance(layers[j].get("weights_of"), bool) \
+                        and 0 <= layers[j]["weights_of"] < len(layers) and hops < len(layers):
+                    j, hops = layers[j]["weights_of"], hops + 1
                 m = dict(layer["mixer"])
                 for key, stem in (("decay_rank", "a1"), ("gate_rank", "g1")):
                     shape = shapes.get(f"l{j}.mix.{stem}")
@@ -199,26 +201,33 @@ class PifazenConfig:
             "suffixes": SUFFIXES})
 
     def _owners(self) -> Tuple[int, ...]:
-        """For every layer the layer whose tensors it runs on (itself, or the ``weights_of`` it names)."""
+        """For every layer the layer whose tensors it runs on: itself, or the ``weights_of`` it names (followed through, if that
+        layer names another in turn)."""
         out = []
         for i, layer in enumerate(self.layers):
             if not isinstance(layer, Mapping):
                 raise ConfigError(f"config.json: layers[{i}] must be an object")
-            src = layer.get("weights_of")
+            src, seen = layer.get("weights_of"), {i}
             if src is None:
                 out.append(i)
                 continue
-            if isinstance(src, bool) or not isinstance(src, int) or not 0 <= src < len(self.layers) or src == i:
-                raise ConfigError(f"config.json: layers[{i}].weights_of {src!r} must name another layer")
-            other = self.layers[src]
-            if not isinstance(other, Mapping) or other.get("weights_of") is not None:
-                raise ConfigError(f"config.json: layers[{i}].weights_of names layer {src}, which has no tensors of its own")
+            while True:
+                if isinstance(src, bool) or not isinstance(src, int) or not 0 <= src < len(self.layers) or src in seen:
+                    raise ConfigError(f"config.json: layers[{i}].weights_of {layer.get('weights_of')!r} must lead to another layer with tensors of its own")
+                other = self.layers[src]
+                if not isinstance(other, Mapping):
+                    raise ConfigError(f"config.json: layers[{src}] must be an object")
+                if other.get("weights_of") is None:
+                    break
+                seen.add(src)
+                src = other.get("weights_of")
             for key in ("type", "mlp"):
                 if other.get(key) != layer.get(key):
                     raise ConfigError(f"config.json: layers[{i}].'{key}' differs from layer {src}'s, whose tensors this layer uses")
             mine, theirs = layer.get("mixer"), other.get("mixer")
+            ranks = ("decay_rank", "gate_rank")
             if not isinstance(mine, Mapping) or not isinstance(theirs, Mapping) or \
-                    {k: v for k, v in mine.items() if k not in ("decay_rank", "gate_rank")} != {k: v for k, v in theirs.items() if k not in ("decay_rank", "gate_rank")}:
+                    {k: v for k, v in mine.items() if k not in ranks} != {k: v for k, v in theirs.items() if k not in ranks}:
                 raise ConfigError(f"config.json: layers[{i}].'mixer' differs from layer {src}'s, whose tensors this layer uses")
             out.append(src)
         return tuple(out)

@@ -406,11 +406,11 @@ LI_EXPORT int li_glu_clamped(const void* gate_up, void* out, int dtype, int T, i
 // PolyNorm and a sigmoid gate.
 //   li_polynorm: per token row z [n]: out = a N(z) + b N(z^2) + c N(z^3) + e with powers element by element and
 //     N(v) = v / sqrt(mean(v^2) + eps); coef = {a, b, c, e} float on the device.  The three means are taken in one pass (the row
-//     in registers up to 8,192 elements, else read again), everything in float, one rounding.
+//     in registers up to 16,384 elements, else read again), everything in float, one rounding.
 //   li_mul_sigmoid: x[t, i] *= sigmoid(gate[t, gate_off + i / group]) in float, one rounding (an output gate per element, or
 //     with group = a head's width one per head).
 namespace {
-constexpr int kPolyRegs = 8;
+constexpr int kPolyRegs = 16;
 
 template <typename T>
 __global__ void polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps, T* __restrict__ out, int n) {

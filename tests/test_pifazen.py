@@ -484,6 +484,11 @@ def test_configuration_is_read_and_refused():
     broken(lambda c: c["layers"][0].update(type="attention"))
     broken(lambda c: c["layers"][0]["mlp"].update(kind="glu"))
     broken(lambda c: c["layers"][3].update(weights_of=3))
+    broken(lambda c: (c["layers"][3].update(weights_of=1), c["layers"][1].update(weights_of=3)))       # a circle
+    # a layer may name a layer that names another: it runs on the tensors at the end of that chain
+    chain = json.loads(json.dumps(cfg))
+    chain["layers"].append(dict(chain["layers"][3], weights_of=3))
+    assert [e.block for e in config_from_dict(chain).to_model_spec().schedule] == [0, 1, 2, 1, 3, 1]
     broken(lambda c: c["layers"][3].update(weights_of=0))                       # another type than its own
     broken(lambda c: c["layers"][3]["mixer"].update(heads=8))                   # other sizes than the layer it names
     broken(lambda c: c["layers"][1]["mlp"]["router"].update(top=5))             # more than the kept groups hold
@@ -608,7 +613,7 @@ def test_gated_delta_rule_kernels(heads, kv, d, dv, taps, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,n", [(5, 24), (3, 1000), (2, 9000)])
+@pytest.mark.parametrize("T,n", [(5, 24), (3, 1000), (2, 9000), (2, 20000)])
 def test_polynorm_kernel(T, n, dtype):
     import kernel_refs as R
     from litinfer_b200 import kernels as K
