@@ -393,32 +393,74 @@ def test_a_token_far_back_reaches_the_last_logits_through_the_state_and_a_far_ke
     assert float((run.logits("a")[-1] - run.logits("b")[-1]).abs().max()) > 0.5 * moved
 
 
-@pytest.mark.parametrize("device", DEVICES)
-def test_a_far_latent_key_with_one_score_made_to_stand_out(device, folders, request):
-    """Model level, latent attention alone, float32: the rotated key part of one far token and every later query's rotated
-    part are made large along one pair of elements at a frequency that is practically zero, so that token's score stands
-    out wherever it lies (the first token, a page's last and first place); the plain model and the engine must agree, and
-    the far token must move the last logits."""
-    dev = use_device(device, request)
-    folder, cfg, w = folders["latent_only"]
+def _weights_with_one_key_that_stands_out(cfg, w, hot_token):
+    """Latent attention alone, weights changed by hand so that one token's key draws every later query: residual channel 0
+    carries a constant that every token's query latent passes on to element 0 of each head's query, residual channel 1 is
+    zero but for ``hot_token``, whose key latent passes it on to element 0 of each head's key."""
+    w = {k: v.clone() for k, v in w.items()}
     m = cfg["layers"][0]["mixer"]
+    H, d, dr = m["heads"], m["dim"], m["rot_dim"]
+    w["embed"][:, 0] = 3.0
+    w["embed"][:, 1] = 0.0
+    w["embed"][hot_token, 1] = 6.0
+    w["l0.norm1"][:2] = 0.0
+    for name in ("l0.mix.dq", "l0.mix.dkv", "l0.mix.g"):
+        w[name][:, :2] = 0.0                       # nothing else reads the two channels
+    w["l0.mix.dq"][0] = 0.0
+    w["l0.mix.dq"][0, 0] = 1.0                     # query latent 0 = the constant
+    w["l0.mix.dkv"][0] = 0.0
+    w["l0.mix.dkv"][0, 1] = 1.0                    # key/value latent 0 = the hot token's mark
+    w["l0.mix.dq.norm"][0] = 1.0
+    w["l0.mix.dkv.norm"][0] = 1.0
+    for h in range(H):
+        w["l0.mix.uq"][h * (d + dr)] = 0.0
+        w["l0.mix.uq"][h * (d + dr), 0] = 8.0      # element 0 of every head's query
+        w["l0.mix.uk"][h * d] = 0.0
+        w["l0.mix.uk"][h * d, 0] = 8.0             # element 0 of every head's key
+    w["l0.mix.uq"][:, 0] = torch.where(torch.arange(w["l0.mix.uq"].shape[0]) % (d + dr) == 0, w["l0.mix.uq"][:, 0], torch.zeros(()))
+    w["l0.mix.uk"][:, 0] = torch.where(torch.arange(w["l0.mix.uk"].shape[0]) % d == 0, w["l0.mix.uk"][:, 0], torch.zeros(()))
+    w["l0.mix.uv"][:, 0] = 2.0                     # and its value is unmistakable
+    return w
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_a_far_latent_key_with_one_score_made_to_stand_out(device, tmp_path, request):
+    """Model level, latent attention alone, float32.  Random weights would bury one far key among hundreds, so the weights
+    are made by hand (see above): the marked token's score stands out by tens of units for every later query, wherever it
+    lies (the first place, a page's last and first place, far back, just before the decoded tokens).  Moving the mark by one
+    place must move the logits of exactly the queries between the two places, in the plain model and in the engine alike, in
+    a prompt's portion and in tokens decoded one by one."""
+    from litinfer_b200.weights.safetensors_io import write_file
+
+    dev = use_device(device, request)
+    cfg = CONFIGS["latent_only"]
+    hot_token = cfg["vocab"] - 1
+    w = _weights_with_one_key_that_stands_out(cfg, make_weights("latent_only", 900), hot_token)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    write_file(tmp_path / "model.safetensors", w)
+    w64 = {k: v.double() for k, v in w.items()}
     n = 200 if device == "cuda" else 70
-    base = random_tokens(n, cfg["vocab"], 77)
-    for hot in (0, 15, 16, n - 8):
+    base = [t if t != hot_token else 0 for t in random_tokens(n, cfg["vocab"], 77)]
+    for hot in (0, 15, 16, n // 2, n - 8):
         toks = list(base)
-        toks[hot] = cfg["vocab"] - 1                       # a token no other place holds
-        toks = [t if (i == hot or t != cfg["vocab"] - 1) else 0 for i, t in enumerate(toks)]
-        other = list(toks)
-        other[hot] = cfg["vocab"] - 2
-        ra = oracle("latent_only", cfg, w, toks, "float32")
-        rb = oracle("latent_only", cfg, w, other, "float32")
-        run = Run(folder, "float32", dev, 256, graphs=False)
-        run.step([("a", toks, n - 5)])
-        for i in range(5):
+        toks[hot] = hot_token
+        ref = P.forward(cfg, w64, toks).float()
+        plain = P.forward(cfg, w64, base).float()
+        moved = (ref - plain).abs().max(dim=-1).values
+        assert float(moved[:hot].max() if hot else 0.0) < 1e-9 and float(moved[hot:].min()) > 0.5, f"mark at {hot}: the plain model does not see it as made"
+        run = Run(tmp_path, "float32", dev, 256, graphs=False)
+        run.step([("a", toks, n - 12)])
+        for i in range(12):
             run.step([("a", toks, 1)])
-        assert_close(run.logits("a"), ra, "float32", f"hot key at {hot}")
-        assert float((ra[-1] - rb[-1]).abs().max()) > 1e-3, f"the token at {hot} does not reach the last logits of the plain model"
-    assert m["rot_dim"] > 0
+        assert_close(run.logits("a"), ref, "float32", f"mark at {hot}")
+        # in portions that end right at the mark and right behind it
+        cuts = [c for c in (hot, hot + 1) if 0 < c < n]
+        at = 0
+        for c in cuts + [n]:
+            if c > at:
+                run.step([("b", toks, c - at)])
+                at = c
+        assert_close(run.logits("b"), ref, "float32", f"mark at {hot}, portions cut around it")
 
 
 @pytest.mark.gpu
