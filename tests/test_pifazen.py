@@ -451,14 +451,14 @@ def test_a_far_latent_key_with_one_score_made_to_stand_out(device, tmp_path, req
         run = Run(tmp_path, "float32", dev, 256, graphs=False)
         run.step([("a", toks, n - 12)])
         for i in range(12):
-            run.step([("a", toks, 1)])
+            run.step([("a", toks, 1)], end=["a"] if i == 11 else [])
         assert_close(run.logits("a"), ref, "float32", f"mark at {hot}")
         # in portions that end right at the mark and right behind it
         cuts = [c for c in (hot, hot + 1) if 0 < c < n]
         at = 0
         for c in cuts + [n]:
             if c > at:
-                run.step([("b", toks, c - at)])
+                run.step([("b", toks, c - at)], end=["b"] if c == n else [])
                 at = c
         assert_close(run.logits("b"), ref, "float32", f"mark at {hot}, portions cut around it")
 
